@@ -25,7 +25,17 @@
 // among several blocks and a small kernel puts their shares together.  Blocks find their work from the step's request
 // table themselves, so a launch depends on the step's shape only.
 //
-// Compile with -DTKB_QK=<query/key size> -DTKB_VD=<value size>.
+// A second weight function, chosen at compile time (-DTKB_SIGMOID=1): no softmax, the weight of a visible key is
+// sigmoid(s_ij), not normalised over the keys (no sink, no running maximum; partial sums of blocks and warps simply add).
+// In both forms a head may carry a factor on its scale and a number added to its scores (head_scale, head_bias:
+// float32 [heads] or null): s_ij = cap(scale * head_scale_h * q_i . k_j) + head_bias_h.
+//
+// sink_attn_prep can also scale the normed q and k heads by weight vectors, rotate them by position (pairs of
+// neighbouring channels or of the two halves of the first rot_dims channels; angles, sines and cosines float64, made
+// once a token), and cache the key as projected (before norm and rotation) as the value (values_are_keys: QK == VD, the
+// projections hold no v).
+//
+// Compile with -DTKB_QK=<query/key size> -DTKB_VD=<value size> [-DTKB_SIGMOID=1].
 #include "common.cuh"
 #include <float.h>
 
@@ -33,6 +43,9 @@
 #error "compile with -DTKB_QK=<query/key size> -DTKB_VD=<value size>"
 #endif
 static_assert(TKB_QK >= 1 && TKB_QK <= 512 && TKB_VD >= 1 && TKB_VD <= 512, "head sizes up to 512");
+#ifndef TKB_SIGMOID
+#define TKB_SIGMOID 0
+#endif
 
 using namespace tkb;
 
@@ -43,6 +56,7 @@ constexpr int VD = TKB_VD;
 constexpr int ROW = QK + VD;
 constexpr int WARPS = 4;
 constexpr int DPL = (VD + 31) / 32;
+constexpr bool SIGMOID = TKB_SIGMOID != 0;
 
 template <typename T>
 __device__ __forceinline__ float dot_key(const T* __restrict__ k, const float* __restrict__ q) {
@@ -77,14 +91,17 @@ __device__ __forceinline__ float dot_key(const T* __restrict__ k, const float* _
   return acc;
 }
 
-// qkv: float32 [T, stride] = [q (nh * QK) | k (nkv * QK) | v (nkv * VD)]
+// qkv: float32 [T, stride] = [q (nh * QK) | k (nkv * QK) | v (nkv * VD)]  (no v if values_are_keys)
+// norm_w: float32 [2][QK] weights of the q heads' and the k heads' norm, or null; freq: float64 [rot_dims / 2] or null
 template <typename T>
 __global__ void __launch_bounds__(256)
 sink_attn_prep_kernel(const float* __restrict__ qkv, int stride, const float* __restrict__ bias, int unit_norm,
                       float eps, T* __restrict__ q_out, T* __restrict__ cache, const int* __restrict__ positions,
                       const int* __restrict__ token_seq, const int* __restrict__ page_indptr,
                       const int* __restrict__ page_ids, int nh, int nkv, int page_size, int num_pages, int write_cache,
-                      int* __restrict__ status) {
+                      int* __restrict__ status, const float* __restrict__ norm_w, const double* __restrict__ freq,
+                      int rot_dims, int rot_pairs, int values_are_keys) {
+  __shared__ float rot_cs[QK];  // [rot_dims / 2] cosines, then as many sines
   trigger_dependents();
   grid_dependency_wait();
   const int t = blockIdx.x;
@@ -96,6 +113,16 @@ sink_attn_prep_kernel(const float* __restrict__ qkv, int stride, const float* __
   int page = -1;
   if (write_cache) page = checked_page(page_ids[page_indptr[s] + p / page_size], num_pages, status);
   const int slot = p % page_size;
+  const int half = freq != nullptr ? rot_dims / 2 : 0;
+  if (half > 0) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      double sn, cs;
+      sincos((double)p * freq[i], &sn, &cs);
+      rot_cs[i] = (float)cs;
+      rot_cs[half + i] = (float)sn;
+    }
+    __syncthreads();
+  }
   // q heads and k heads: one warp a head
   for (int hh = warp; hh < nh + nkv; hh += nwarps) {
     const int off = hh * QK;  // k heads follow the q heads in the row
@@ -109,11 +136,20 @@ sink_attn_prep_kernel(const float* __restrict__ qkv, int stride, const float* __
     T* dst = nullptr;
     if (hh < nh) dst = q_out + (size_t)t * nh * QK + off;
     else if (page >= 0) dst = cache + (((size_t)page * nkv + (hh - nh)) * page_size + slot) * ROW;
-    if (dst != nullptr)
-      for (int d = lane; d < QK; d += 32) dst[d] = from_float<T>((row[off + d] + (bias ? bias[off + d] : 0.f)) * r);
+    if (dst != nullptr) {
+      const float* w = norm_w ? norm_w + (hh < nh ? 0 : QK) : nullptr;
+      auto val = [&](int d) { return (row[off + d] + (bias ? bias[off + d] : 0.f)) * r * (w ? w[d] : 1.f); };
+      for (int i = lane; i < half; i += 32) {
+        const int a = rot_pairs ? 2 * i : i, b = rot_pairs ? 2 * i + 1 : i + half;
+        const float u = val(a), v = val(b), c = rot_cs[i], sn = rot_cs[half + i];
+        dst[a] = from_float<T>(u * c - v * sn);
+        dst[b] = from_float<T>(v * c + u * sn);
+      }
+      for (int d = 2 * half + lane; d < QK; d += 32) dst[d] = from_float<T>(val(d));
+    }
   }
   if (page >= 0) {
-    const int voff = (nh + nkv) * QK;
+    const int voff = values_are_keys ? nh * QK : (nh + nkv) * QK;  // the keys as projected are the values
     for (int idx = threadIdx.x; idx < nkv * VD; idx += blockDim.x) {
       const int g = idx / VD, d = idx - g * VD;
       cache[(((size_t)page * nkv + g) * page_size + slot) * ROW + QK + d] =
@@ -128,7 +164,8 @@ attn_sink_simt_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __r
                       const int* __restrict__ token_seq, const int* __restrict__ positions,
                       const int* __restrict__ page_indptr, const int* __restrict__ page_ids,
                       const int* __restrict__ rows, const float* __restrict__ sinks, int nh, int nkv, int page_size,
-                      float scale, float softcap, int window, int num_pages, int* __restrict__ status) {
+                      float scale, float softcap, int window, int num_pages, int* __restrict__ status,
+                      const float* __restrict__ head_scale, const float* __restrict__ head_bias) {
   __shared__ float qs[WARPS][QK];
   trigger_dependents();
   grid_dependency_wait();
@@ -150,6 +187,7 @@ attn_sink_simt_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __r
     for (int d = lane; d < QK; d += 32) qs[warp][d] = to_float(qrow[d]);
     __syncwarp();
 
+    const float hscale = scale * (head_scale ? head_scale[h] : 1.f), hbias = head_bias ? head_bias[h] : 0.f;
     // the sink opens the running softmax: maximum sink, sum exp(sink - sink) = 1, nothing accumulated
     float m = sinks ? sinks[h] : -FLT_MAX;
     float l = sinks ? 1.f : 0.f;
@@ -167,19 +205,25 @@ attn_sink_simt_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __r
         const int page = checked_page(table[j / page_size], num_pages, status);
         if (page >= 0) {  // else: an id beyond the pool (the status flag is set); the key counts for nothing
           rowoff = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * ROW;
-          sc = dot_key<T>(cache + rowoff, qs[warp]) * scale;
+          sc = dot_key<T>(cache + rowoff, qs[warp]) * hscale;
           if (softcap > 0.f) sc = softcap * tanhf(sc * inv_cap);
+          sc += hbias;
           counted = true;
         }
       }
-      const float bm = warp_max(sc);
-      const float m_new = fmaxf(m, bm);
-      const float alpha = expf(m - m_new);
-      const float pj = counted ? expf(sc - m_new) : 0.f;
-      l = l * alpha + warp_sum(pj);
-      m = m_new;
+      float pj;
+      if constexpr (SIGMOID) {
+        pj = counted ? 1.f / (1.f + expf(-sc)) : 0.f;
+      } else {
+        const float bm = warp_max(sc);
+        const float m_new = fmaxf(m, bm);
+        const float alpha = expf(m - m_new);
+        pj = counted ? expf(sc - m_new) : 0.f;
+        l = l * alpha + warp_sum(pj);
+        m = m_new;
 #pragma unroll
-      for (int i = 0; i < DPL; i++) acc[i] *= alpha;
+        for (int i = 0; i < DPL; i++) acc[i] *= alpha;
+      }
       const int nlive = (p - base + 1) < 32 ? (p - base + 1) : 32;
       for (int jj = 0; jj < nlive; jj++) {
         const float pv = __shfl_sync(0xffffffffu, pj, jj);
@@ -192,7 +236,7 @@ attn_sink_simt_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __r
         }
       }
     }
-    const float inv_l = l > 0.f ? 1.f / l : 0.f;
+    const float inv_l = SIGMOID ? 1.f : (l > 0.f ? 1.f / l : 0.f);
     T* orow = out + ((size_t)blockIdx.x * nh + h) * VD;
 #pragma unroll
     for (int i = 0; i < DPL; i++) {
@@ -206,25 +250,28 @@ attn_sink_simt_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __r
 template <typename T>
 int prep_launch(const float* qkv, int stride, const float* bias, int unit_norm, float eps, void* q_out, void* cache,
                 const int* positions, const int* token_seq, const int* page_indptr, const int* page_ids, int n_tokens,
-                int nh, int nkv, int page_size, int num_pages, int write_cache, int* status, cudaStream_t st) {
+                int nh, int nkv, int page_size, int num_pages, int write_cache, int* status, const float* norm_w,
+                const double* freq, int rot_dims, int rot_pairs, int values_are_keys, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || page_size <= 0) return -2;
+  if (freq != nullptr && (rot_dims < 0 || rot_dims > QK || (rot_dims & 1))) return -2;
+  if (values_are_keys && QK != VD) return -2;
   return launch_pdl(sink_attn_prep_kernel<T>, dim3(n_tokens), dim3(256), 0, st, qkv, stride, bias, unit_norm, eps,
                     (T*)q_out, (T*)cache, positions, token_seq, page_indptr, page_ids, nh, nkv, page_size, num_pages,
-                    write_cache, status);
+                    write_cache, status, norm_w, freq, rot_dims, rot_pairs, values_are_keys);
 }
 
 template <typename T>
 int attn_launch(const void* q, void* out, const void* cache, const int* token_seq, const int* positions,
                 const int* page_indptr, const int* page_ids, const int* rows, int n_rows, const float* sinks, int nh,
                 int nkv, int page_size, float scale, float softcap, int window, int num_pages, int* status,
-                cudaStream_t st) {
+                const float* head_scale, const float* head_bias, cudaStream_t st) {
   if (n_rows <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return -2;
   if (nkv > 65535) return -3;
   return launch_pdl(attn_sink_simt_kernel<T>, dim3(n_rows, nkv), dim3(WARPS * 32), 0, st, (const T*)q, (T*)out,
                     (const T*)cache, token_seq, positions, page_indptr, page_ids, rows, sinks, nh, nkv, page_size,
-                    scale, softcap, window, num_pages, status);
+                    scale, softcap, window, num_pages, status, head_scale, head_bias);
 }
 
 }  // namespace
@@ -233,17 +280,21 @@ int attn_launch(const void* q, void* out, const void* cache, const int* token_se
   TKB_EXPORT int tkb_sink_attn_prep_##SUF(const float* qkv, int stride, const float* bias, int unit_norm, float eps,  \
                                           void* q_out, void* cache, const int* positions, const int* token_seq,       \
                                           const int* page_indptr, const int* page_ids, int n_tokens, int nh, int nkv, \
-                                          int page_size, int num_pages, int write_cache, int* status, void* st) {     \
+                                          int page_size, int num_pages, int write_cache, int* status,                 \
+                                          const float* norm_w, const double* freq, int rot_dims, int rot_pairs,       \
+                                          int values_are_keys, void* st) {                                            \
     return prep_launch<T>(qkv, stride, bias, unit_norm, eps, q_out, cache, positions, token_seq, page_indptr,         \
-                          page_ids, n_tokens, nh, nkv, page_size, num_pages, write_cache, status, (cudaStream_t)st);  \
+                          page_ids, n_tokens, nh, nkv, page_size, num_pages, write_cache, status, norm_w, freq,       \
+                          rot_dims, rot_pairs, values_are_keys, (cudaStream_t)st);                                    \
   }                                                                                                                   \
   TKB_EXPORT int tkb_attn_sink_simt_##SUF(const void* q, void* out, const void* cache, const int* token_seq,          \
                                           const int* positions, const int* page_indptr, const int* page_ids,          \
                                           const int* rows, int n_rows, const float* sinks, int nh, int nkv,           \
                                           int page_size, float scale, float softcap, int window, int num_pages,       \
-                                          int* status, void* st) {                                                    \
+                                          int* status, const float* head_scale, const float* head_bias, void* st) {   \
     return attn_launch<T>(q, out, cache, token_seq, positions, page_indptr, page_ids, rows, n_rows, sinks, nh, nkv,   \
-                          page_size, scale, softcap, window, num_pages, status, (cudaStream_t)st);                    \
+                          page_size, scale, softcap, window, num_pages, status, head_scale, head_bias,                \
+                          (cudaStream_t)st);                                                                          \
   }
 
 TKB_SINK_EXPORTS(f32, float)
@@ -291,23 +342,30 @@ __device__ __forceinline__ float ex2(float x) {
 // tanh = 1, one that underflows tanh = -1, as they should.  The exponential and the reciprocal are each good to about
 // 1e-7 of a result near 1, so the capped score is off by about cap * 1e-7: the size of a float32 rounding of a score of
 // the cap's own size (the FP32-pipe kernel calls tanhf).  Without a cap: d * scale * log2(e).
+// A number added to the score (a head's bias) enters as b2 = bias log2(e).
 struct ScoreMap {
-  float k1, c0, c1;  // capped: fma(rcp(ex2(k1 d) + 1), c1, c0) with c0 = cap log2(e), c1 = -2 c0;  plain: d * k1
+  float k1, c0, c1;  // capped: fma(rcp(ex2(k1 d) + 1), c1, c0) with c0 = cap log2(e) + b2, c1 = -2 cap log2(e);  plain: d * k1 + c0
   bool capped;
 };
-__device__ __forceinline__ ScoreMap score_map(float scale, float softcap) {
+__device__ __forceinline__ ScoreMap score_map(float scale, float softcap, float bias = 0.f) {
   ScoreMap m;
   m.capped = softcap > 0.f;
   m.k1 = m.capped ? 2.f * LOG2E * scale / softcap : scale * LOG2E;
-  m.c0 = softcap * LOG2E;
-  m.c1 = -2.f * m.c0;
+  m.c0 = (m.capped ? softcap * LOG2E : 0.f) + bias * LOG2E;
+  m.c1 = -2.f * softcap * LOG2E;
   return m;
 }
 __device__ __forceinline__ float mapped_score(float d, const ScoreMap& m) {
-  if (!m.capped) return d * m.k1;
+  if (!m.capped) return fmaf(d, m.k1, m.c0);
   float r;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(ex2(d * m.k1) + 1.f));
   return fmaf(r, m.c1, m.c0);
+}
+// sigmoid of a score given in units of log2: 1 / (1 + 2^(-x)); an exponential that overflows gives 0
+__device__ __forceinline__ float sigmoid2(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(ex2(-x) + 1.f));
+  return r;
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -338,7 +396,7 @@ __device__ __forceinline__ void stage_tile(bf16* buf, const bf16* __restrict__ c
 template <int NT, bool MASKED>
 __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const uint32_t (&qf)[KSTEPS][4], float (&o)[VT][4],
                                        float (&m)[2], float (&l)[2], const int (&lim_lo)[2], const int (&lim_hi)[2],
-                                       const ScoreMap& sm, int lane) {
+                                       const ScoreMap (&sm)[2], int lane) {
   const int g = lane >> 2, t = lane & 3;
   float sc[NT][4];
 #pragma unroll
@@ -364,6 +422,22 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
       }
     }
   }
+  if constexpr (SIGMOID) {
+    // no softmax: a key's weight is the sigmoid of its score, keys out of sight weigh nothing; m and l stay as they are
+#pragma unroll
+    for (int h = 0; h < 2; h++)
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          float v = sigmoid2(mapped_score(sc[nt][h * 2 + e], sm[h]));
+          if (MASKED) {
+            const int key = key0 + nt * 8 + 2 * t + e;
+            if (key < lim_lo[h] || key > lim_hi[h]) v = 0.f;
+          }
+          sc[nt][h * 2 + e] = v;
+        }
+  } else {
   float alpha[2];
 #pragma unroll
   for (int h = 0; h < 2; h++) {
@@ -372,7 +446,7 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
     for (int nt = 0; nt < NT; nt++)
 #pragma unroll
       for (int e = 0; e < 2; e++) {
-        float v = mapped_score(sc[nt][h * 2 + e], sm);
+        float v = mapped_score(sc[nt][h * 2 + e], sm[h]);
         if (MASKED) {
           const int key = key0 + nt * 8 + 2 * t + e;
           if (key < lim_lo[h] || key > lim_hi[h]) v = -INFINITY;
@@ -403,6 +477,7 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
     o[vt][2] *= alpha[1];
     o[vt][3] *= alpha[1];
   }
+  }
 #pragma unroll
   for (int kk = 0; kk < NT / 2; kk++) {  // 16 keys at a time
     uint32_t pf[4] = {pack_bf16(sc[2 * kk][0], sc[2 * kk][1]), pack_bf16(sc[2 * kk][2], sc[2 * kk][3]),
@@ -427,7 +502,8 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                        const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                        const int* __restrict__ page_ids, int n_seqs, const float* __restrict__ sinks, int nh, int nkv,
-                       int ps, float scale, float softcap, int window, int num_pages, int* __restrict__ status) {
+                       int ps, float scale, float softcap, int window, int num_pages, int* __restrict__ status,
+                       const float* __restrict__ head_scale, const float* __restrict__ head_bias) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* bufs = reinterpret_cast<bf16*>(smem_raw);
   trigger_dependents();
@@ -447,7 +523,8 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
   const int r0 = tile * KT;              // first query of the tile within the portion
   const int rows = min(KT, n_q - r0);
   const int* table = page_ids + page_indptr[s];
-  const ScoreMap sm = score_map(scale, softcap);
+  const ScoreMap sm1 = score_map(scale * (head_scale ? head_scale[h] : 1.f), softcap, head_bias ? head_bias[h] : 0.f);
+  const ScoreMap sm[2] = {sm1, sm1};
 
   uint32_t qf[KSTEPS][4];
   int lim_lo[2], lim_hi[2];
@@ -465,9 +542,11 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
       qf[ks][hh + 2] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
     }
   }
-  const float sink2 = sinks ? sinks[h] * LOG2E : NEG_BIG;
+  // (the sigmoid form never touches m and l: a sum of 1 makes the division at the end the identity)
+  const float sink2 = SIGMOID ? 0.f : (sinks ? sinks[h] * LOG2E : NEG_BIG);
+  const bool open = SIGMOID || sinks != nullptr;
   float m[2] = {sink2, sink2};
-  float l[2] = {(sinks && t == 0) ? 1.f : 0.f, (sinks && t == 0) ? 1.f : 0.f};
+  float l[2] = {(open && t == 0) ? 1.f : 0.f, (open && t == 0) ? 1.f : 0.f};
   float o[VT][4];
 #pragma unroll
   for (int vt = 0; vt < VT; vt++) o[vt][0] = o[vt][1] = o[vt][2] = o[vt][3] = 0.f;
@@ -528,7 +607,8 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
                         const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_ids, const float* __restrict__ sinks, int nh, int nkv, int head_tiles,
                         int ps, float scale, float softcap, int window, int num_pages, int* __restrict__ status,
-                        float* __restrict__ part) {
+                        float* __restrict__ part, const float* __restrict__ head_scale,
+                        const float* __restrict__ head_bias) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* bufs = reinterpret_cast<bf16*>(smem_raw);
   trigger_dependents();
@@ -543,7 +623,7 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
   const int tok = seq_q_start[s];
   const int p = seq_kv_len[s] - 1;
   const int* table = page_ids + page_indptr[s];
-  const ScoreMap sm = score_map(scale, softcap);
+  ScoreMap sm[2];
   const int k_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
 
   uint32_t qf[KSTEPS][4];
@@ -560,8 +640,10 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
       qf[ks][hh] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
       qf[ks][hh + 2] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
     }
-    m[hh] = sinks ? sinks[head] * LOG2E : NEG_BIG;
-    l[hh] = (sinks && split == 0 && warp == 0 && t == 0) ? 1.f : 0.f;  // the sink counts once: in one warp's sums
+    sm[hh] = score_map(scale * (head_scale ? head_scale[head] : 1.f), softcap, head_bias ? head_bias[head] : 0.f);
+    // (the sigmoid form: every share has maximum 0, and ONE share carries the sum 1, so the merges below only add)
+    m[hh] = SIGMOID ? 0.f : (sinks ? sinks[head] * LOG2E : NEG_BIG);
+    l[hh] = ((SIGMOID || sinks) && split == 0 && warp == 0 && t == 0) ? 1.f : 0.f;  // the sink counts once: in one warp's sums
   }
   float o[VT][4];
 #pragma unroll
@@ -672,7 +754,8 @@ TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache
                                      const int* seq_q_len, const int* seq_kv_len, const int* page_indptr,
                                      const int* page_ids, int n_tokens, int n_seqs, int portions, int singles,
                                      const float* sinks, int nh, int nkv, int page_size, float scale, float softcap,
-                                     int window, int num_pages, int* status, float* part, int splits, void* st) {
+                                     int window, int num_pages, int* status, float* part, int splits,
+                                     const float* head_scale, const float* head_bias, void* st) {
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return -2;
   const int head_tiles = (nh / nkv + 15) / 16;
@@ -689,7 +772,8 @@ TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache
   if (singles) {
     rc = launch_pdl(attn_sink_single_kernel, dim3(n_seqs, nkv * head_tiles, splits), dim3(128), TC_SMEM, (cudaStream_t)st,
                     (const bf16*)q, (bf16*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr,
-                    page_ids, sinks, nh, nkv, head_tiles, page_size, scale, softcap, window, num_pages, status, part);
+                    page_ids, sinks, nh, nkv, head_tiles, page_size, scale, softcap, window, num_pages, status, part,
+                    head_scale, head_bias);
     if (rc == 0 && splits > 1)
       rc = launch_pdl(attn_sink_merge_kernel, dim3(n_seqs, nh), dim3(VD >= 128 ? 128 : 64), 0, (cudaStream_t)st,
                       (const float*)part, (bf16*)out, seq_q_start, seq_q_len, nh, splits);
@@ -698,7 +782,7 @@ TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache
   const int tiles = n_tokens / KT + n_seqs;  // no step of this shape has more 64-query tiles
   return launch_pdl(attn_sink_tiles_kernel, dim3(tiles, nh), dim3(128), TC_SMEM, (cudaStream_t)st, (const bf16*)q,
                     (bf16*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, n_seqs,
-                    sinks, nh, nkv, page_size, scale, softcap, window, num_pages, status);
+                    sinks, nh, nkv, page_size, scale, softcap, window, num_pages, status, head_scale, head_bias);
 }
 #endif  // tensor-core sizes
 TKB_EXPORT int tkb_attn_sink_has_tc() {

@@ -8,12 +8,16 @@
 //   * the selective state space (state-space duality form): a_t = exp(-exp(A_head) dt_t), c_t = dt_t, k = B, q = C
 //     shared by the heads of a group, v = x, D a number per head; x, B and C come out of a causal convolution over
 //     time with bias and SiLU, dt_t = softplus(dt_raw + dt_bias).
+//   * gated linear attention: a DIFFERENT decay for every key channel, S_t = diag(f_t) S_(t-1) + k_t v_t^T, with
+//     f_t = sigmoid(A2 (A1 h_t) + b)^(1/tau) made beforehand for all tokens (gla_gates, which also scales q);
+//   * retention: a_t = lambda_head, q and k rotated by position and k scaled beforehand (rotate_scale).
 // Everything here is float32: projections arrive as float32 rows, the state lives in the request's slot as S^T,
 // state[slot][head][vdim][dim], and the outputs leave as float32 rows for the norm that follows.
 //
 // Kernels: ssm_prep (convolution + SiLU for every channel of [x | B | C], dt and the decay; one block a token; inputs
 // from before the step come from the request's carried inputs), conv_carry (brings the carried inputs forward after
-// every token has read them), decay_walk (the recurrence).
+// every token has read them), decay_walk (the recurrence; a build of it with a decay vector a token and head),
+// gla_gates, rotate_scale.
 //
 // The walk: one block owns some columns of the state of one (request, head) and goes over the request's tokens of
 // this step in order.  LANES threads share a column j of S (lane L holds dims 4 (L + LANES i) .. + 3): a step is 2 DPT
@@ -126,8 +130,11 @@ __global__ void silu_cols_kernel(float* __restrict__ x, int stride, int ncols) {
 // a token, decay and key scale a float a token each.
 constexpr int QROW = LANES * DPT;
 
+// VEC: a decay for every key channel, fvec [T, heads * dim] rows of f_stride floats, staged beside q and k.
+template <bool VEC>
 __global__ void __launch_bounds__(1024)
 decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __restrict__ k, int k_stride, int qk_div,
+                  const float* __restrict__ fvec, int f_stride,
                   const float* __restrict__ v, int v_stride, const float* __restrict__ dt_dec,
                   const float* __restrict__ decay_head, const float* __restrict__ skip, float* __restrict__ state,
                   long long slot_stride, float* __restrict__ out, const int* __restrict__ seq_slot,
@@ -136,7 +143,8 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
   extern __shared__ __align__(16) float smem[];
   const int cols = min(cols_per_block, vdim);
   const int cols4 = (cols + 3) & ~3;
-  const int buf_floats = chunk * (2 * QROW + cols4 + 2);
+  constexpr int NQ = VEC ? 3 : 2;  // staged rows of QROW floats a token: q, k (and the decays)
+  const int buf_floats = chunk * (NQ * QROW + cols4 + 2);
   float* os = smem + 2 * buf_floats;  // the lanes' shares of a chunk's outputs: [cols][LANES][chunk + 1]
   const int orow = chunk + 1;         // (one float of padding: the lanes of a column write different banks)
   const int s = blockIdx.x, head = blockIdx.y;
@@ -174,6 +182,7 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
   }
   const float* qh = q + (size_t)(head / qk_div) * dim;
   const float* kh = k + (size_t)(head / qk_div) * dim;
+  const float* fh = VEC ? fvec + (size_t)head * dim : nullptr;
   const float* vh = v + (size_t)head * vdim + col_begin;
   const float a_const = decay_head ? decay_head[head] : 1.f;
   const float d_skip = skip ? skip[head] : 0.f;
@@ -182,7 +191,8 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
   auto stage = [&](int t0, int b) {
     float* qs = smem + b * buf_floats;
     float* ks = qs + chunk * QROW;
-    float* vs = ks + chunk * QROW;
+    float* fs = ks + chunk * QROW;  // (VEC only)
+    float* vs = qs + NQ * chunk * QROW;
     float* as = vs + chunk * cols4;
     float* cs = as + chunk;
     const int nt = min(chunk, n - t0);
@@ -192,12 +202,14 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
         const int t = idx / d4n, d4 = idx - t * d4n;
         cp_async16(qs + t * QROW + 4 * d4, qh + (size_t)(start + t0 + t) * q_stride + 4 * d4);
         cp_async16(ks + t * QROW + 4 * d4, kh + (size_t)(start + t0 + t) * k_stride + 4 * d4);
+        if (VEC) cp_async16(fs + t * QROW + 4 * d4, fh + (size_t)(start + t0 + t) * f_stride + 4 * d4);
       }
     } else {
       for (int idx = tid; idx < nt * dim; idx += blockDim.x) {
         const int t = idx / dim, d = idx - t * dim;
         cp_async4(qs + t * QROW + d, qh + (size_t)(start + t0 + t) * q_stride + d);
         cp_async4(ks + t * QROW + d, kh + (size_t)(start + t0 + t) * k_stride + d);
+        if (VEC) cp_async4(fs + t * QROW + d, fh + (size_t)(start + t0 + t) * f_stride + d);
       }
     }
     if (vec_v && (ncols & 3) == 0) {
@@ -234,7 +246,8 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
     __syncthreads();
     const float* qs = smem + b * buf_floats;
     const float* ks = qs + chunk * QROW;
-    const float* vs = ks + chunk * QROW;
+    const float* fs = ks + chunk * QROW;
+    const float* vs = qs + NQ * chunk * QROW;
     const float* as = vs + chunk * cols4;
     const float* cs = as + chunk;
     float* mine = os + (lc * LANES + lane) * orow;
@@ -243,16 +256,25 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
       const float a = dt_dec ? as[t] : a_const, ck = dt_dec ? cs[t] : 1.f;
       const float4* q4 = reinterpret_cast<const float4*>(qs + t * QROW) + lane;
       const float4* k4 = reinterpret_cast<const float4*>(ks + t * QROW) + lane;
+      const float4* f4 = reinterpret_cast<const float4*>(fs + t * QROW) + lane;
       const float vj = lc < ncols ? vs[t * cols4 + lc] : 0.f;
       const float cv = ck * vj;
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
       for (int i = 0; i < DPT / 4; i++) {
         const float4 qq = q4[LANES * i], kk = k4[LANES * i];
-        S[4 * i + 0] = fmaf(a, S[4 * i + 0], kk.x * cv);
-        S[4 * i + 1] = fmaf(a, S[4 * i + 1], kk.y * cv);
-        S[4 * i + 2] = fmaf(a, S[4 * i + 2], kk.z * cv);
-        S[4 * i + 3] = fmaf(a, S[4 * i + 3], kk.w * cv);
+        if (VEC) {
+          const float4 ff = f4[LANES * i];
+          S[4 * i + 0] = fmaf(ff.x, S[4 * i + 0], kk.x * cv);
+          S[4 * i + 1] = fmaf(ff.y, S[4 * i + 1], kk.y * cv);
+          S[4 * i + 2] = fmaf(ff.z, S[4 * i + 2], kk.z * cv);
+          S[4 * i + 3] = fmaf(ff.w, S[4 * i + 3], kk.w * cv);
+        } else {
+          S[4 * i + 0] = fmaf(a, S[4 * i + 0], kk.x * cv);
+          S[4 * i + 1] = fmaf(a, S[4 * i + 1], kk.y * cv);
+          S[4 * i + 2] = fmaf(a, S[4 * i + 2], kk.z * cv);
+          S[4 * i + 3] = fmaf(a, S[4 * i + 3], kk.w * cv);
+        }
         a0 = fmaf(S[4 * i + 0], qq.x, a0);
         a1 = fmaf(S[4 * i + 1], qq.y, a1);
         a2 = fmaf(S[4 * i + 2], qq.z, a2);
@@ -305,7 +327,8 @@ decay_walk_kernel(const float* __restrict__ q, int q_stride, const float* __rest
   }
 }
 
-int walk_launch(const float* q, int q_stride, const float* k, int k_stride, int qk_div, const float* v, int v_stride,
+int walk_launch(const float* q, int q_stride, const float* k, int k_stride, int qk_div, const float* fvec, int f_stride,
+                const float* v, int v_stride,
                 const float* dt_dec, const float* decay_head, const float* skip, float* state, long long slot_stride,
                 float* out, const int* seq_slot, const int* seq_q_start, const int* seq_q_len, int n_seqs, int n_tokens,
                 int heads, int dim, int vdim, int write_state, cudaStream_t st) {
@@ -322,21 +345,30 @@ int walk_launch(const float* q, int q_stride, const float* k, int k_stride, int 
   if (splits > 65535) return -3;
   const int threads = ((cols_per_block * LANES + 31) / 32) * 32;
   const int cols4 = (cols_per_block + 3) & ~3;
-  const size_t smem = (size_t)(2 * chunk * (2 * QROW + cols4 + 2) + cols_per_block * LANES * (chunk + 1)) * sizeof(float);
+  const int nq = fvec != nullptr ? 3 : 2;
+  const size_t smem = (size_t)(2 * chunk * (nq * QROW + cols4 + 2) + cols_per_block * LANES * (chunk + 1)) * sizeof(float);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(decay_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = fvec != nullptr
+                        ? cudaFuncSetAttribute(decay_walk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                        : cudaFuncSetAttribute(decay_walk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  const int vec_qk = dim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && al16(q) && al16(k);
+  const int vec_qk = dim % 4 == 0 && q_stride % 4 == 0 && k_stride % 4 == 0 && al16(q) && al16(k) &&
+                     (fvec == nullptr || (f_stride % 4 == 0 && al16(fvec)));
   const int vec_v = vdim % 4 == 0 && v_stride % 4 == 0 && cols_per_block % 4 == 0 && al16(v);
   const int vec_s = dim % 4 == 0 && slot_stride % 4 == 0 && al16(state);
   // An ordinary launch, not a programmatic one: blocks that come onto the SMs while the kernel ahead still holds some of
   // them are placed where room happens to be, several to an SM, and this kernel's few long-lived blocks then run on a
   // part of the GPU (measured: 0.84 ms instead of 0.36 ms for 2,048 tokens of 16 heads).
-  decay_walk_kernel<<<dim3(n_seqs, heads, splits), dim3(threads), smem, st>>>(
-      q, q_stride, k, k_stride, qk_div, v, v_stride, dt_dec, decay_head, skip, state, slot_stride, out, seq_slot,
-      seq_q_start, seq_q_len, heads, dim, vdim, write_state, cols_per_block, vec_qk, vec_v, vec_s, chunk);
+  if (fvec != nullptr)
+    decay_walk_kernel<true><<<dim3(n_seqs, heads, splits), dim3(threads), smem, st>>>(
+        q, q_stride, k, k_stride, qk_div, fvec, f_stride, v, v_stride, dt_dec, decay_head, skip, state, slot_stride, out,
+        seq_slot, seq_q_start, seq_q_len, heads, dim, vdim, write_state, cols_per_block, vec_qk, vec_v, vec_s, chunk);
+  else
+    decay_walk_kernel<false><<<dim3(n_seqs, heads, splits), dim3(threads), smem, st>>>(
+        q, q_stride, k, k_stride, qk_div, fvec, f_stride, v, v_stride, dt_dec, decay_head, skip, state, slot_stride, out,
+        seq_slot, seq_q_start, seq_q_len, heads, dim, vdim, write_state, cols_per_block, vec_qk, vec_v, vec_s, chunk);
   return launch_status();
 }
 
@@ -360,13 +392,15 @@ TKB_EXPORT int tkb_ssm_prep(const float* proj, int stride, int xbc_off, int C, i
 }
 
 // dt_dec: float32 [T, 2 * heads] (key scale, then decay) or null, then decay_head [heads] is the decay and the key
-// scale is 1.  skip: [heads] or null.
-TKB_EXPORT int tkb_decay_walk(const float* q, int q_stride, const float* k, int k_stride, int qk_div, const float* v,
-                              int v_stride, const float* dt_dec, const float* decay_head, const float* skip,
+// scale is 1; or fvec [T, heads * dim] (rows of f_stride floats): a decay for every key channel, key scale 1 (then
+// dt_dec and decay_head are null).  skip: [heads] or null.
+TKB_EXPORT int tkb_decay_walk(const float* q, int q_stride, const float* k, int k_stride, int qk_div, const float* fvec,
+                              int f_stride, const float* v, int v_stride, const float* dt_dec, const float* decay_head, const float* skip,
                               float* state, long long slot_stride, float* out, const int* seq_slot,
                               const int* seq_q_start, const int* seq_q_len, int n_seqs, int n_tokens, int heads, int dim,
                               int vdim, int write_state, void* st) {
-  return walk_launch(q, q_stride, k, k_stride, qk_div, v, v_stride, dt_dec, decay_head, skip, state, slot_stride, out,
+  if (fvec != nullptr && (dt_dec != nullptr || qk_div != 1)) return -2;
+  return walk_launch(q, q_stride, k, k_stride, qk_div, fvec, f_stride, v, v_stride, dt_dec, decay_head, skip, state, slot_stride, out,
                      seq_slot, seq_q_start, seq_q_len, n_seqs, n_tokens, heads, dim, vdim, write_state, (cudaStream_t)st);
 }
 
@@ -375,4 +409,112 @@ TKB_EXPORT int tkb_silu_cols(float* x, int stride, int ncols, int rows, void* st
   int threads = 32;
   while (threads < ncols / 4 && threads < 512) threads <<= 1;
   return launch_pdl(silu_cols_kernel, dim3(rows), dim3(threads), 0, (cudaStream_t)st, x, stride, ncols);
+}
+
+namespace {
+
+// Decays of gated linear attention for GT tokens a block: z[c] = b[c] + sum_r A2t[r][c] low[t][r] (A2t float32
+// [rank, C], the transposed second factor; low = A1 h, rank columns of the projections), f = sigmoid(z)^(1/tau) =
+// exp(log_sigmoid(z) / tau) with log_sigmoid(z) = min(z, 0) - log1p(exp(-|z|)); and q (q_cols columns at q_off of
+// the same rows) times q_scale, in place.
+constexpr int GT = 8;
+__global__ void __launch_bounds__(256)
+gla_gates_kernel(float* __restrict__ proj, int stride, int low_off, int rank, const float* __restrict__ a2t,
+                 const float* __restrict__ bias, float inv_tau, int C, float* __restrict__ f, int q_off, int q_cols,
+                 float q_scale, int n_tokens) {
+  extern __shared__ float low[];  // [GT][rank]
+  trigger_dependents();
+  grid_dependency_wait();
+  const int t0 = blockIdx.x * GT;
+  const int nt = min(GT, n_tokens - t0);
+  for (int idx = threadIdx.x; idx < nt * rank; idx += blockDim.x) {
+    const int t = idx / rank, r = idx - t * rank;
+    low[idx] = proj[(size_t)(t0 + t) * stride + low_off + r];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float z[GT];
+    const float b = bias ? bias[c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < GT; t++) z[t] = b;
+    for (int r = 0; r < rank; r++) {
+      const float w = a2t[(size_t)r * C + c];
+#pragma unroll
+      for (int t = 0; t < GT; t++)
+        if (t < nt) z[t] = fmaf(w, low[t * rank + r], z[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < GT; t++)
+      if (t < nt) f[(size_t)(t0 + t) * C + c] = expf((fminf(z[t], 0.f) - log1pf(expf(-fabsf(z[t])))) * inv_tau);
+  }
+  if (q_scale != 1.f)
+    for (int idx = threadIdx.x; idx < nt * q_cols; idx += blockDim.x) {
+      const int t = idx / q_cols, c = idx - t * q_cols;
+      proj[(size_t)(t0 + t) * stride + q_off + c] *= q_scale;
+    }
+}
+
+// Rotation by position of the q and k heads of float32 rows, in place: the first rot_dims channels of a head, channel i
+// paired with i + rot_dims / 2 (pairs == 0) or channel 2i with 2i + 1 (pairs != 0); (u, v) -> (u cos a - v sin a,
+// v cos a + u sin a), a = position * freq[i].  The angle, sine and cosine are float64 (the float32 product of a
+// position in the thousands and a frequency is off by 1e-4 of a radian), made once a token for all heads.  Then q
+// times q_scale and k times k_scale.  One block a token.
+__global__ void __launch_bounds__(256)
+rotate_scale_kernel(float* __restrict__ proj, int stride, int q_off, int k_off, int heads, int dim, int rot_dims,
+                    int pairs, const double* __restrict__ freq, const int* __restrict__ positions,
+                    const int* __restrict__ token_seq, float q_scale, float k_scale) {
+  extern __shared__ float cs[];  // [rot_dims / 2] cosines, then as many sines
+  trigger_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  if (token_seq[t] < 0) return;
+  const int half = rot_dims / 2;
+  const double p = (double)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double s, c;
+    sincos(p * freq[i], &s, &c);
+    cs[i] = (float)c;
+    cs[half + i] = (float)s;
+  }
+  __syncthreads();
+  float* row = proj + (size_t)t * stride;
+  const int per_head = dim - half;  // a thread's items a head: `half` pairs, then the channels that pass
+  for (int idx = threadIdx.x; idx < 2 * heads * per_head; idx += blockDim.x) {
+    const int which = idx / (heads * per_head);
+    const int rem = idx - which * heads * per_head;
+    const int h = rem / per_head, i = rem - h * per_head;
+    float* x = row + (which ? k_off : q_off) + (size_t)h * dim;
+    const float sc = which ? k_scale : q_scale;
+    if (i < half) {
+      const int a = pairs ? 2 * i : i, b = pairs ? 2 * i + 1 : i + half;
+      const float u = x[a], v = x[b], c = cs[i], s = cs[half + i];
+      x[a] = (u * c - v * s) * sc;
+      x[b] = (v * c + u * s) * sc;
+    } else if (sc != 1.f) {
+      x[rot_dims + (i - half)] *= sc;
+    }
+  }
+}
+
+}  // namespace
+
+TKB_EXPORT int tkb_gla_gates(float* proj, int stride, int low_off, int rank, const float* a2t, const float* bias,
+                             float inv_tau, int C, float* f, int q_off, int q_cols, float q_scale, int n_tokens,
+                             void* st) {
+  if (n_tokens <= 0) return 0;
+  if (rank <= 0 || C <= 0 || (size_t)GT * rank * sizeof(float) > 48 * 1024) return -2;
+  return launch_pdl(gla_gates_kernel, dim3((n_tokens + GT - 1) / GT), dim3(256), (size_t)GT * rank * sizeof(float),
+                    (cudaStream_t)st, proj, stride, low_off, rank, a2t, bias, inv_tau, C, f, q_off, q_cols, q_scale,
+                    n_tokens);
+}
+
+TKB_EXPORT int tkb_rotate_scale(float* proj, int stride, int q_off, int k_off, int heads, int dim, int rot_dims,
+                                int pairs, const double* freq, const int* positions, const int* token_seq,
+                                float q_scale, float k_scale, int n_tokens, void* st) {
+  if (n_tokens <= 0) return 0;
+  if (heads <= 0 || dim <= 0 || rot_dims < 0 || rot_dims > dim || (rot_dims & 1) || (size_t)rot_dims * 4 > 48 * 1024)
+    return -2;
+  return launch_pdl(rotate_scale_kernel, dim3(n_tokens), dim3(256), (size_t)rot_dims * sizeof(float), (cudaStream_t)st,
+                    proj, stride, q_off, k_off, heads, dim, rot_dims, pairs, freq, positions, token_seq, q_scale,
+                    k_scale);
 }

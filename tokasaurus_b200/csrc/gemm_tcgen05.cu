@@ -11,7 +11,8 @@
 //            memory, i.e. 32 rows of the tile) and store the epilogue's result, while the MMAs of the next
 //            tile fill the second accumulator buffer.
 // Epilogues: bfloat16 store; or, for a weight that interleaves gate and up rows in groups of 8,
-// silu(gate) * up as bfloat16 [M, N/2] (the activation pass over memory disappears).
+// silu(gate) * up as bfloat16 [M, N/2] (the activation pass over memory disappears); or, for an ungated weight, the
+// exact (erf) GELU of the product.
 //
 // No load uses cluster multicast.  Every wait on an mbarrier is bounded: after the limit the block sets
 // TKB_STATUS_WAIT_TIMEOUT in the status word, stops waiting, frees its tensor memory and returns.
@@ -41,7 +42,8 @@ template <int BN, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ out, int ldo, int M, int N, int K, int* __restrict__ status,
-                    const int* __restrict__ tile_group, int group_rows, float act_limit, float act_alpha) {
+                    const int* __restrict__ tile_group, int group_rows, float act_limit, float act_alpha,
+                    int plain_act) {
   extern __shared__ unsigned char smem_raw[];
   constexpr int STAGES = Cfg<BN>::STAGES;
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
@@ -147,6 +149,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), r);
         if (row < M) {
           if (!GATED) {
+            if (plain_act == 1) {  // exact GELU of every value before it is stored
+#pragma unroll
+              for (int jj = 0; jj < 32; jj++) {
+                const float v = __uint_as_float(r[jj]);
+                r[jj] = __float_as_uint(0.5f * v * (1.f + erff(v * 0.70710678118654752f)));
+              }
+            }
             const int n = n0 + c0;
             bf16* dst = out + (size_t)row * ldo + n;
             if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
@@ -211,7 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int BN, bool GATED>
 int launch(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M, int N, int K, int* status,
            cudaStream_t st, const int* tile_group = nullptr, int groups = 1, float act_limit = 0.f,
-           float act_alpha = 0.f) {
+           float act_alpha = 0.f, int plain_act = 0) {
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -228,7 +237,7 @@ int launch(const void* A, int lda, const void* W, int ldw, void* out, int ldo, i
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   dim3 grid(tiles < n_sms ? tiles : n_sms);
   gemm_tcgen05_kernel<BN, GATED><<<grid, THREADS, Cfg<BN>::SMEM_BYTES, st>>>(map_a, map_w, (bf16*)out, ldo, M, N, K, status,
-                                                                                 tile_group, N, act_limit, act_alpha);
+                                                                                 tile_group, N, act_limit, act_alpha, plain_act);
   return launch_status();
 }
 
@@ -270,9 +279,12 @@ TKB_EXPORT int tkb_gemm_tcgen05_clamped_bf16(const void* A, int lda, const void*
 // Grouped form: W is [groups * N, K], rows g * N .. (g + 1) * N the weights of group g, and row tile i of A (128
 // rows) multiplies the weights of group tile_group[i] (a device array of ceil(M / 128) entries; -1: the tile is
 // nobody's and is left out).  The caller orders A's rows by group and starts every group on a tile boundary.
+// gated: 0 plain, 1 silu(gate) * up over interleaved rows, 2 plain with the exact GELU of every result.
 TKB_EXPORT int tkb_gemm_tcgen05_grouped_bf16(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
                                              int N, int K, int gated, const int* tile_group, int groups, int* status,
                                              void* st_) {
+  const int plain_act = gated == 2 ? 1 : 0;
+  if (gated == 2) gated = 0;
   cudaStream_t st = (cudaStream_t)st_;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return -2;
@@ -281,8 +293,8 @@ TKB_EXPORT int tkb_gemm_tcgen05_grouped_bf16(const void* A, int lda, const void*
   if (rc) return rc;
   if (N >= 256) {
     return gated ? launch<256, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups)
-                 : launch<256, false>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups);
+                 : launch<256, false>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups, 0.f, 0.f, plain_act);
   }
   return gated ? launch<128, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups)
-               : launch<128, false>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups);
+               : launch<128, false>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups, 0.f, 0.f, plain_act);
 }

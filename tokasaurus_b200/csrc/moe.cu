@@ -2,6 +2,11 @@
 // the chosen ones (float32), the ordering of a step's (token, choice) pairs by expert, the experts' products over
 // that ordering (each block finds its expert from the offsets on the device, so nothing is read back to the host),
 // and the weighted sum of the chosen experts' outputs.  Built for float and bfloat16 activations.
+//
+// A second way of choosing (moe_choose_scored): scores s = sigmoid(logits); the choice goes by s + correction (a
+// learned vector that takes no part in the weights), among the experts of the best `keep` of `groups` equal groups of
+// neighbours only (a group scores the sum of its two largest choice scores); the weights are the chosen experts' s over
+// their sum (+ 1e-20), times a scale.  A second kind of expert: down(gelu(up h)) with the exact (erf) GELU, no gate.
 #include "common.cuh"
 #include <float.h>
 
@@ -111,6 +116,95 @@ moe_choose_kernel(const float* __restrict__ z_all, const int* __restrict__ token
   for (int k = lane; k < top; k += 32) top_w[(size_t)t * top + k] *= inv;
 }
 
+// Router, second kernel, the other way of choosing: one warp a token.  s = sigmoid(z), c = s + correction; group g holds
+// experts g * per .. (g + 1) * per - 1 and scores the sum of its two largest c (its only c if per == 1); experts
+// outside the `keep` best groups cannot be chosen (their c counts as minus infinity); the `top` largest c are chosen,
+// equal scores: the lower expert (group) first; weights s / (sum of the chosen s + 1e-20) * scale.
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_choose_scored_kernel(const float* __restrict__ z_all, const float* __restrict__ correction,
+                         const int* __restrict__ token_seq, int* __restrict__ top_idx, float* __restrict__ top_w,
+                         int n_tokens, int E, int top, int groups, int keep, float scale) {
+  extern __shared__ float zs[];  // [warps][2 E + groups]: s, c, group scores
+  trigger_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
+  if (t >= n_tokens) return;
+  if (token_seq != nullptr && token_seq[t] < 0) {
+    for (int k = lane; k < top; k += 32) {
+      top_idx[(size_t)t * top + k] = -1;
+      top_w[(size_t)t * top + k] = 0.f;
+    }
+    return;
+  }
+  float* sv = zs + (size_t)warp * (2 * E + groups);
+  float* cv = sv + E;
+  float* gs = cv + E;
+  for (int e = lane; e < E; e += 32) {
+    const float s = 1.f / (1.f + expf(-z_all[(size_t)t * E + e]));
+    sv[e] = s;
+    cv[e] = s + (correction != nullptr ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  auto warp_argmax = [&](float& best, int& arg) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+  };
+  if (groups > 1 && keep < groups) {
+    const int per = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float b1 = -FLT_MAX, b2 = -FLT_MAX;
+      for (int e = g * per; e < (g + 1) * per; e++) {
+        const float v = cv[e];
+        if (v > b1) { b2 = b1; b1 = v; }
+        else if (v > b2) b2 = v;
+      }
+      gs[g] = per > 1 ? b1 + b2 : b1;
+    }
+    __syncwarp();
+    // take the `keep` best groups one after the other; a group that is taken gets the mark +inf
+    for (int k = 0; k < keep; k++) {
+      float best = -FLT_MAX;
+      int arg = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && v > best) { best = v; arg = g; }
+      }
+      warp_argmax(best, arg);
+      if (lane == 0 && arg < groups) gs[arg] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gs[e / per] != INFINITY) cv[e] = -INFINITY;
+    __syncwarp();
+  }
+  float denom = 0.f;
+  for (int k = 0; k < top; k++) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = cv[e];
+      if (v > best) { best = v; arg = e; }
+    }
+    warp_argmax(best, arg);
+    const float w = arg < E ? sv[arg] : 0.f;
+    denom += w;
+    __syncwarp();
+    if (lane == 0) {
+      top_idx[(size_t)t * top + k] = arg < E ? arg : -1;
+      top_w[(size_t)t * top + k] = w;
+      if (arg < E) cv[arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  const float f = scale / (denom + 1e-20f);
+  for (int k = lane; k < top; k += 32) top_w[(size_t)t * top + k] *= f;
+}
+
 // One block: offsets[e] .. is expert e's span of the ordering; order[p] is the (token, choice) pair at place p
 // (token * top + choice), place_of[pair] its place (-1 for a padding token's pairs).  pad > 1: every span starts at
 // a multiple of pad (the tensor-core product's row tile), offsets[e + 1] - offsets[e] is then the span with its
@@ -188,14 +282,18 @@ __global__ void moe_gather_kernel(const T* __restrict__ src, const int* __restri
 // sequential chain over K, whatever else is in the step):
 //   plain:  C[p, n] = A[src(p), :] . W[e][n, :]                      (C float32 [places, N])
 //   gated:  C[p, n] = silu(A[src(p), :] . W[e][n, :]) * (A[src(p), :] . W[e][N + n, :])      (W[e] is [2N, K])
+//   gelu:   C[p, n] = gelu(A[src(p), :] . W[e][n, :]), the exact (erf) form, in A's type
 // src(p) = order[p] / top if `order` is given (rows of the step's tokens), else p.  Block (x, y): column tile x of the
 // y-th row tile, counted over the experts' spans in turn; blocks beyond the last tile leave at once.
 constexpr int BM = 64, BN = 64, BK = 16;
+constexpr int ACT_NONE = 0, ACT_GATED = 1, ACT_GELU = 2;
+__device__ __forceinline__ float gelu_erf_f(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
 
-template <typename TA, typename TC, bool GATED>
+template <typename TA, typename TC, int ACT>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC* __restrict__ C, int ldc,
                 const int* __restrict__ offsets, const int* __restrict__ order, int top, int E, int N, int K) {
+  constexpr bool GATED = ACT == ACT_GATED;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   __shared__ float Us[GATED ? BK : 1][BN + 4];
@@ -273,6 +371,7 @@ moe_gemm_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC*
       if (n >= N) continue;
       float v = acc[i][j];
       if (GATED) v = v / (1.f + expf(-v)) * acu[i][j];
+      if (ACT == ACT_GELU) v = gelu_erf_f(v);
       C[(size_t)p * ldc + n] = from_float<TC>(v);
     }
   }
@@ -307,10 +406,11 @@ template <> struct Vec8<float> {
   }
 };
 
-template <typename TA, typename TC, bool GATED>
+template <typename TA, typename TC, int ACT>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 moe_gemv_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC* __restrict__ C, int ldc,
                 const int* __restrict__ offsets, const int* __restrict__ order, int top, int N, int K) {
+  constexpr bool GATED = ACT == ACT_GATED;
   trigger_dependents();
   grid_dependency_wait();
   const int e = blockIdx.y;
@@ -372,6 +472,7 @@ moe_gemv_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC*
               const float u = warp_sum(acu[j][r]);
               v = v / (1.f + expf(-v)) * u;
             }
+            if (ACT == ACT_GELU) v = gelu_erf_f(v);
             const int f = f0 + j;
             if (lane == 0 && f < N) C[(size_t)(r0 + r) * ldc + f] = from_float<TC>(v);
           }
@@ -416,7 +517,24 @@ int route_launch(const void* h, const float* wr, const float* br, const int* tok
                     (const float*)logits, token_seq, top_idx, top_w, n_tokens, E, top);
 }
 
-template <typename TA, typename TC, bool GATED>
+template <typename T>
+int route_scored_launch(const void* h, const float* wr, const float* br, const float* correction, const int* token_seq,
+                        int* top_idx, float* top_w, float* logits, int n_tokens, int H, int E, int top, int groups,
+                        int keep, float scale, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
+      top > keep * (E / groups) || (size_t)(2 * E + groups) * 4 * ROUTE_WARPS > 48 * 1024 || (E + 3) / 4 > 65535)
+    return -2;
+  const int tb = (n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
+  int rc = launch_pdl(moe_logits_kernel<T>, dim3(tb, (E + 3) / 4), dim3(ROUTE_WARPS * 32), 0, st, (const T*)h, wr, br,
+                      logits, n_tokens, H, E);
+  if (rc != 0) return rc;
+  return launch_pdl(moe_choose_scored_kernel, dim3(tb), dim3(ROUTE_WARPS * 32),
+                    (size_t)ROUTE_WARPS * (2 * E + groups) * sizeof(float), st, (const float*)logits, correction,
+                    token_seq, top_idx, top_w, n_tokens, E, top, groups, keep, scale);
+}
+
+template <typename TA, typename TC, int ACT>
 int gemm_launch(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets, const int* order, int top,
                 int n_places, int E, int N, int K, cudaStream_t st) {
   if (n_places <= 0 || N <= 0) return 0;
@@ -424,11 +542,11 @@ int gemm_launch(const void* A, int lda, const void* W, void* C, int ldc, const i
   // few rows: every weight once, at full width (rows of 8 values must start on 16 bytes)
   const bool wide = K % 8 == 0 && lda % 8 == 0 && (((uintptr_t)A) & 15) == 0 && (((uintptr_t)W) & 15) == 0;
   if (wide && n_places <= GEMV_PLACES_MAX && E <= 65535)
-    return launch_pdl(moe_gemv_kernel<TA, TC, GATED>, dim3((N + GV_FEATS - 1) / GV_FEATS, E), dim3(GV_WARPS * 32), 0, st,
+    return launch_pdl(moe_gemv_kernel<TA, TC, ACT>, dim3((N + GV_FEATS - 1) / GV_FEATS, E), dim3(GV_WARPS * 32), 0, st,
                       (const TA*)A, lda, (const TA*)W, (TC*)C, ldc, offsets, order, top, N, K);
   const int row_tiles = n_places / BM + E;  // sum over experts of ceil(count / BM) is at most this
   if (row_tiles > 65535) return -3;
-  return launch_pdl(moe_gemm_kernel<TA, TC, GATED>, dim3((N + BN - 1) / BN, row_tiles), dim3(256), 0, st, (const TA*)A,
+  return launch_pdl(moe_gemm_kernel<TA, TC, ACT>, dim3((N + BN - 1) / BN, row_tiles), dim3(256), 0, st, (const TA*)A,
                     lda, (const TA*)W, (TC*)C, ldc, offsets, order, top, E, N, K);
 }
 
@@ -459,11 +577,23 @@ TKB_EXPORT int tkb_moe_order(const int* top_idx, int n_pairs, int E, int top, in
   }                                                                                                                    \
   TKB_EXPORT int tkb_moe_gemm_gated_##SUF(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets, \
                                           const int* order, int top, int n_places, int E, int N, int K, void* st) {    \
-    return gemm_launch<T, T, true>(A, lda, W, C, ldc, offsets, order, top, n_places, E, N, K, (cudaStream_t)st);       \
+    return gemm_launch<T, T, ACT_GATED>(A, lda, W, C, ldc, offsets, order, top, n_places, E, N, K, (cudaStream_t)st);  \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_moe_gemm_gelu_##SUF(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets,  \
+                                         const int* order, int top, int n_places, int E, int N, int K, void* st) {     \
+    return gemm_launch<T, T, ACT_GELU>(A, lda, W, C, ldc, offsets, order, top, n_places, E, N, K, (cudaStream_t)st);   \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_moe_route_scored_##SUF(const void* h, const float* wr, const float* br, const float* correction,  \
+                                            const int* token_seq, int* top_idx, float* top_w, float* logits,           \
+                                            int n_tokens, int H, int E, int top, int groups, int keep, float scale,    \
+                                            void* st) {                                                                \
+    return route_scored_launch<T>(h, wr, br, correction, token_seq, top_idx, top_w, logits, n_tokens, H, E, top,       \
+                                  groups, keep, scale, (cudaStream_t)st);                                              \
   }                                                                                                                    \
   TKB_EXPORT int tkb_moe_gemm_##SUF(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets,       \
                                     const int* order, int top, int n_places, int E, int N, int K, void* st) {          \
-    return gemm_launch<T, float, false>(A, lda, W, C, ldc, offsets, order, top, n_places, E, N, K, (cudaStream_t)st);  \
+    return gemm_launch<T, float, ACT_NONE>(A, lda, W, C, ldc, offsets, order, top, n_places, E, N, K,                  \
+                                           (cudaStream_t)st);                                                          \
   }                                                                                                                    \
   TKB_EXPORT int tkb_moe_combine_##SUF(const float* y, const int* place_of, const float* top_w, const void* shared_t,  \
                                        const float* shared_slices, int n_slices, long long slice_stride, void* out,    \
@@ -487,4 +617,12 @@ TKB_EXPORT int tkb_moe_combine_y16_bf16(const void* y, const int* place_of, cons
                                         int n_tokens, int H, int top, void* st) {
   return combine_launch<__nv_bfloat16, __nv_bfloat16>(y, place_of, top_w, shared_t, shared_slices, n_slices, slice_stride,
                                                       out, n_tokens, H, top, (cudaStream_t)st);
+}
+
+// ... and its sum as float32 rows, for a consumer that reads float32 (a norm).
+TKB_EXPORT int tkb_moe_combine_y16_f32(const void* y, const int* place_of, const float* top_w, const void* shared_t,
+                                       const float* shared_slices, int n_slices, long long slice_stride, void* out,
+                                       int n_tokens, int H, int top, void* st) {
+  return combine_launch<float, __nv_bfloat16>(y, place_of, top_w, shared_t, shared_slices, n_slices, slice_stride, out,
+                                              n_tokens, H, top, (cudaStream_t)st);
 }

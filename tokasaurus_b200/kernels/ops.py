@@ -906,9 +906,12 @@ def latent_attn(q_abs: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, cac
 # ---------------------------------------------------------------------------------------------
 # Routed experts (csrc/moe.cu)
 def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: torch.Tensor | None, token_seq: torch.Tensor,
-              top: int, top_idx: torch.Tensor, top_w: torch.Tensor) -> None:
+              top: int, top_idx: torch.Tensor, top_w: torch.Tensor, scored: dict | None = None) -> None:
     """Router logits h @ router_w^T + router_b in float32, the ``top`` largest per token (int32 [T, top]) and the
-    softmax over them (float32 [T, top])."""
+    softmax over them (float32 [T, top]).  ``scored`` = dict(correction float32 [E] or None, groups, keep, scale): the
+    other way of choosing: scores sigmoid(logits); the choice by score + correction among the experts of the best
+    ``keep`` of ``groups`` equal groups of neighbours (a group scores the sum of its two largest choice scores); the
+    weights are the chosen scores over their sum, times ``scale``."""
     _need_cuda(h, router_w, router_b, token_seq, top_idx, top_w)
     T, H = h.shape
     E = router_w.shape[0]
@@ -917,8 +920,20 @@ def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: torch.Tensor | 
     _need(router_b is None or (router_b.dtype == torch.float32 and router_b.numel() == E), "moe_route: bias float32 [E]")
     _need(top_idx.dtype == torch.int32 and top_w.dtype == torch.float32 and tuple(top_idx.shape) == (T, top)
           and tuple(top_w.shape) == (T, top) and top_idx.is_contiguous() and top_w.is_contiguous(), "moe_route: outputs [T, top]")
-    f = _fn(_libs.get("moe.cu"), f"tkb_moe_route_{_suffix(h.dtype)}")
     logits = torch.empty((T, E), dtype=torch.float32, device=h.device)
+    if scored is not None:
+        corr, groups, keep = scored.get("correction"), int(scored.get("groups", 1)), int(scored.get("keep", 1))
+        _need_cuda(corr)
+        _need(corr is None or (corr.dtype == torch.float32 and corr.is_contiguous() and corr.numel() == E),
+              "moe_route: correction float32 [E]")
+        _need(groups > 0 and E % groups == 0 and 0 < keep <= groups and top <= keep * (E // groups),
+              f"moe_route: {E} experts in {groups} groups of which {keep} are kept, {top} chosen")
+        f = _fn(_libs.get("moe.cu"), f"tkb_moe_route_scored_{_suffix(h.dtype)}")
+        _check(f(_ptr(h), _ptr(router_w), _ptr(router_b), _ptr(corr), _ptr(token_seq), _ptr(top_idx), _ptr(top_w),
+                 _ptr(logits), c_int(T), c_int(H), c_int(E), c_int(top), c_int(groups), c_int(keep),
+                 c_float(float(scored.get("scale", 1.0))), _stream()), "moe_route")
+        return
+    f = _fn(_libs.get("moe.cu"), f"tkb_moe_route_{_suffix(h.dtype)}")
     _check(f(_ptr(h), _ptr(router_w), _ptr(router_b), _ptr(token_seq), _ptr(top_idx), _ptr(top_w), _ptr(logits), c_int(T),
              c_int(H), c_int(E), c_int(top), _stream()), "moe_route")
 
@@ -958,34 +973,38 @@ def moe_gather(src: torch.Tensor, src_token: torch.Tensor, out: torch.Tensor) ->
 
 
 def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, status: torch.Tensor,
-                         gated: bool = False) -> torch.Tensor:
+                         gated: bool = False, gelu: bool = False) -> torch.Tensor:
     """Row tile i (128 rows) of a[M, K] times the weights w[tile_group[i]] of w [groups, N, K], bfloat16 on the tcgen05
     tensor cores; tiles with tile_group[i] < 0 are left out (their rows of the result are not written).
-    ``gated``: every group's rows interleave gate and up (``interleave_gate_up``); the result is [M, N / 2]."""
+    ``gated``: every group's rows interleave gate and up (``interleave_gate_up``); the result is [M, N / 2].
+    ``gelu`` (ungated): the exact GELU of every result in the epilogue."""
     _need_cuda(a, w, tile_group, status)
     G, N, K = w.shape
     _need(can_use_tcgen05(a, w.view(G * N, K)) and a.shape[1] == K, "gemm_tcgen05_grouped: bfloat16, K a multiple of 8")
     M = a.shape[0]
     _need(tile_group.dtype == torch.int32 and tile_group.numel() * 128 >= M, "gemm_tcgen05_grouped: a group for every row tile")
     _need(not gated or N % 16 == 0, "gemm_tcgen05_grouped: gated rows come in groups of 16")
+    _need(not (gated and gelu), "gemm_tcgen05_grouped: the GELU epilogue is the ungated form's")
     out = torch.empty((M, N // 2 if gated else N), dtype=torch.bfloat16, device=a.device)
     _check(_fn(_libs.get("gemm_tcgen05.cu"), "tkb_gemm_tcgen05_grouped_bf16")(
         _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(K), _ptr(out), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
-        c_int(1 if gated else 0), _ptr(tile_group), c_int(G), _ptr(status), _stream()), "gemm_tcgen05_grouped")
+        c_int(1 if gated else (2 if gelu else 0)), _ptr(tile_group), c_int(G), _ptr(status), _stream()), "gemm_tcgen05_grouped")
     return out
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor | None,
-             top: int, gated: bool) -> None:
+             top: int, gated: bool, gelu: bool = False) -> None:
     """The experts' products over the ordering.  w [E, N (2N if gated), K]; a [., K]; row p of ``out`` is made from
     row order[p] // top of ``a`` (row p if ``order`` is None) with the weights of the expert whose span holds p.
-    gated: out = silu(a w_gate^T) * (a w_up^T) in a's type [places, N]; else float32 [places, N]."""
+    gated: out = silu(a w_gate^T) * (a w_up^T) in a's type [places, N]; gelu: out = gelu(a w^T) (exact) in a's type;
+    else float32 [places, N]."""
     _need_cuda(a, w, out, offsets, order)
     E, NN, K = w.shape
     N = NN // 2 if gated else NN
     _need(a.dtype == w.dtype and a.stride(1) == 1 and a.shape[1] == K and w.is_contiguous(), "moe_gemm: operands")
-    _need(out.shape[1] == N and out.stride(1) == 1 and out.dtype == (a.dtype if gated else torch.float32), "moe_gemm: out")
-    name = f"tkb_moe_gemm_{'gated_' if gated else ''}{_suffix(a.dtype)}"
+    _need(not (gated and gelu), "moe_gemm: gated or gelu")
+    _need(out.shape[1] == N and out.stride(1) == 1 and out.dtype == (a.dtype if (gated or gelu) else torch.float32), "moe_gemm: out")
+    name = f"tkb_moe_gemm_{'gated_' if gated else ('gelu_' if gelu else '')}{_suffix(a.dtype)}"
     _check(_fn(_libs.get("moe.cu"), name)(_ptr(a), c_int(a.stride(0)), _ptr(w), _ptr(out), c_int(out.stride(0)),
                                           _ptr(offsets), _ptr(order), c_int(top), c_int(out.shape[0]), c_int(E), c_int(N),
                                           c_int(K), _stream()), "moe_gemm")
@@ -999,10 +1018,10 @@ def moe_combine(y: torch.Tensor, place_of: torch.Tensor, top_w: torch.Tensor, sh
     T, H = out.shape
     top = top_w.shape[1]
     _need(y.is_contiguous() and y.shape[1] == H and out.is_contiguous(), "moe_combine: y, out")
-    _need(y.dtype == torch.float32 or (y.dtype == torch.bfloat16 and out.dtype == torch.bfloat16),
-          "moe_combine: expert outputs float32, or bfloat16 in a bfloat16 engine")
+    _need(y.dtype in (torch.float32, torch.bfloat16), "moe_combine: expert outputs float32 or bfloat16")
     d, sl, n_sl, stride = _split_update(shared, T, H, out.dtype, "moe_combine")
-    f = _fn(_libs.get("moe.cu"), "tkb_moe_combine_y16_bf16" if y.dtype == torch.bfloat16 else f"tkb_moe_combine_{_suffix(out.dtype)}")
+    f = _fn(_libs.get("moe.cu"), f"tkb_moe_combine_y16_{_suffix(out.dtype)}" if y.dtype == torch.bfloat16
+            else f"tkb_moe_combine_{_suffix(out.dtype)}")
     _check(f(_ptr(y), _ptr(place_of), _ptr(top_w), _ptr(d), _ptr(sl), c_int(n_sl), ctypes.c_longlong(stride), _ptr(out),
              c_int(T), c_int(H), c_int(top), _stream()), "moe_combine")
 
@@ -1073,20 +1092,68 @@ def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: f
                                                 c_float(alpha), c_int(interleave), _stream()), "clamped_glu")
 
 
-def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, groups: int,
-                     eps: float, gate_first: bool) -> None:
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor | None, out: torch.Tensor, groups: int,
+                     eps: float, gate_first: bool, silu_gate: bool = False) -> None:
     """Rows of float32 values, RMS-normed in ``groups`` equal parts and gated: ``gate_first`` False:
-    N(y) * weight * sigmoid(gate); True: N(y * silu(gate)) * weight.  ``y`` and ``gate`` may be column slices of wider
-    float32 tensors."""
+    N(y) * weight * sigmoid(gate) (``silu_gate``: * silu(gate)); True: N(y * silu(gate)) * weight.  ``y`` and ``gate``
+    may be column slices of wider float32 tensors.  ``weight``: a value for every column, or a shorter vector that is
+    used round and round (one part's weights, shared by all parts), or None."""
     _need_cuda(y, gate, weight, out)
     rows, width = y.shape
     _need(y.dtype == torch.float32 and gate.dtype == torch.float32 and y.stride(1) == 1 and gate.stride(1) == 1
           and gate.shape == y.shape, "gated_group_norm: float32 values and gates of one shape")
-    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == width, "gated_group_norm: weight float32 [width]")
+    _need(weight is None or (weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() > 0
+                             and width % weight.numel() == 0), "gated_group_norm: weight float32, a divisor of the width long")
     _need(out.stride(1) == 1 and out.shape == y.shape and groups > 0 and width % groups == 0, "gated_group_norm: out, groups")
+    _need(not (gate_first and silu_gate), "gated_group_norm: the gate first is a SiLU already")
     _check(_fn(_libs.get("post_norm.cu"), f"tkb_gated_group_norm_{_suffix(out.dtype)}")(
-        _ptr(y), c_int(y.stride(0)), _ptr(gate), c_int(gate.stride(0)), _ptr(weight), _ptr(out), c_int(out.stride(0)),
-        c_int(rows), c_int(width), c_int(groups), c_float(eps), c_int(1 if gate_first else 0), _stream()), "gated_group_norm")
+        _ptr(y), c_int(y.stride(0)), _ptr(gate), c_int(gate.stride(0)), _ptr(weight),
+        c_int(weight.numel() if weight is not None else 0), _ptr(out), c_int(out.stride(0)),
+        c_int(rows), c_int(width), c_int(groups), c_float(eps), c_int(1 if gate_first else (2 if silu_gate else 0)),
+        _stream()), "gated_group_norm")
+
+
+def sum_group_norm(x: torch.Tensor, y: torch.Tensor | None, alpha: float, weight: torch.Tensor, eps: float, groups: int,
+                   h_out: torch.Tensor | None = None) -> None:
+    """x = weight * N_g(alpha * x + y) in place (x float32): the norm after the residual sum, each of the row's
+    ``groups`` equal parts divided by its own root mean square.  ``y``: float32 [rows, H], float32 slices
+    [slices, rows, H] of a split product (added in slice order), rows in ``h_out``'s type, or None.  ``h_out``
+    (activation type, x's shape) receives the new x."""
+    _need_cuda(x, y, weight, h_out)
+    rows, H = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "sum_group_norm: x contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == H, "sum_group_norm: weight float32 [H]")
+    _need(groups > 0 and H % groups == 0, f"sum_group_norm: {H} values in {groups} parts")
+    _need(h_out is None or (h_out.shape == x.shape and h_out.is_contiguous()), "sum_group_norm: h_out of x's shape")
+    y32 = y16 = None
+    n_slices = 0
+    if y is not None:
+        _need(y.is_contiguous() and tuple(y.shape[-2:]) == (rows, H), "sum_group_norm: y of x's shape")
+        if y.dtype == torch.float32:
+            y32, n_slices = y, (y.shape[0] if y.dim() == 3 else 1)
+        else:
+            _need(h_out is not None and y.dtype == h_out.dtype and y.dim() == 2, "sum_group_norm: y float32 or in the activation type")
+            y16 = y
+    suf = _suffix(h_out.dtype) if h_out is not None else "f32"
+    _check(_fn(_libs.get("post_norm.cu"), f"tkb_sum_group_norm_{suf}")(
+        _ptr(x), _ptr(y32), c_int(n_slices), ctypes.c_longlong(rows * H), _ptr(y16), c_float(alpha), _ptr(weight),
+        c_float(eps), _ptr(h_out), c_int(rows), c_int(H), c_int(groups), _stream()), "sum_group_norm")
+
+
+def gelu_gate_rows(z: torch.Tensor, table: torch.Tensor, off: int, ids: torch.Tensor, token_seq: torch.Tensor,
+                   seq_slot: torch.Tensor, last_token: torch.Tensor, rows: torch.Tensor | None, out: torch.Tensor,
+                   status: torch.Tensor) -> None:
+    """out[r, j] = gelu_tanh(z[r, j]) * table[token(r), off + j]: z float32 [R, dim]; row r belongs to token rows[r] (r
+    if ``rows`` is None), whose id is found as the embedding finds it (an id < 0: the request's last sampled token)."""
+    _need_cuda(z, table, ids, token_seq, seq_slot, last_token, rows, out, status)
+    R, dim = z.shape
+    _need(z.dtype == torch.float32 and z.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (R, dim)
+          and out.dtype == table.dtype and table.is_contiguous() and off >= 0 and off + dim <= table.shape[1], "gelu_gate_rows: shapes")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.numel() == R), "gelu_gate_rows: rows int32 [R]")
+    _check(_fn(_libs.get("post_norm.cu"), f"tkb_gelu_gate_rows_{_suffix(out.dtype)}")(
+        _ptr(z), _ptr(table), c_int(table.shape[1]), c_int(off), c_int(dim), c_int(table.shape[0]), _ptr(ids),
+        _ptr(token_seq), _ptr(seq_slot), _ptr(last_token), _ptr(rows), _ptr(out), c_int(R), _ptr(status), _stream()),
+        "gelu_gate_rows")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -1163,18 +1230,23 @@ def ssm_prep(proj: torch.Tensor, xbc_off: int, channels: int, conv_w: torch.Tens
 def decay_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads_per_qk: int, dt_dec: torch.Tensor | None,
                decay_head: torch.Tensor | None, skip: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor,
                seq_slot: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor, n_seqs: int, heads: int,
-               dim: int, vdim: int, write_state: bool = True) -> None:
+               dim: int, vdim: int, write_state: bool = True, decay_vec: torch.Tensor | None = None) -> None:
     """S_t = a_t S_(t-1) + (c_t k_t) v_t^T, o_t = S_t^T q_t + skip * v_t over each request's tokens.  q, k [T, . * dim]
     and v [T, heads * vdim] are float32 (column slices allowed); head h reads q and k number h // heads_per_qk.
     ``dt_dec`` [T, 2 heads] = (c, a) per token, or ``decay_head`` [heads] with
-    c = 1.  state float32 [slots, n], S^T of the heads first: [heads, vdim, dim]; out float32 [T, heads * vdim]."""
-    _need_cuda(q, k, v, dt_dec, decay_head, skip, state, out, seq_slot, seq_q_start, seq_q_len)
+    c = 1, or ``decay_vec`` float32 [T, heads * dim] (a column slice allowed): a decay for every key channel,
+    S_t = diag(f_t) S_(t-1) + k_t v_t^T.  state float32 [slots, n], S^T of the heads first: [heads, vdim, dim]; out
+    float32 [T, heads * vdim]."""
+    _need_cuda(q, k, v, dt_dec, decay_head, skip, state, out, seq_slot, seq_q_start, seq_q_len, decay_vec)
     T = q.shape[0]
     for t in (q, k, v):
         _need(t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[0] == T, "decay_walk: float32 rows")
     _need(heads_per_qk > 0 and heads % heads_per_qk == 0 and q.shape[1] == (heads // heads_per_qk) * dim
           and k.shape[1] == q.shape[1] and v.shape[1] == heads * vdim, "decay_walk: shapes of q, k, v")
-    _need((dt_dec is None) != (decay_head is None), "decay_walk: decays per token or per head")
+    _need((dt_dec is not None) + (decay_head is not None) + (decay_vec is not None) == 1,
+          "decay_walk: decays per token, per head or per key channel")
+    _need(decay_vec is None or (decay_vec.dtype == torch.float32 and decay_vec.stride(1) == 1 and heads_per_qk == 1
+                                and tuple(decay_vec.shape) == (T, heads * dim)), "decay_walk: decay_vec float32 [T, heads * dim]")
     _need(dt_dec is None or (dt_dec.dtype == torch.float32 and dt_dec.is_contiguous() and tuple(dt_dec.shape) == (T, 2 * heads)),
           "decay_walk: dt_dec float32 [T, 2 heads]")
     for t in (decay_head, skip):
@@ -1184,10 +1256,48 @@ def decay_walk(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads_per_qk: 
     _need(out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (T, heads * vdim), "decay_walk: out float32 [T, heads * vdim]")
     defines = _walk_defines(dim, vdim, n_seqs * heads * vdim, T == n_seqs, q.device)
     _check(_fn(_libs.get("decay_recurrence.cu", **defines), "tkb_decay_walk")(
-        _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), c_int(heads_per_qk), _ptr(v), c_int(v.stride(0)),
+        _ptr(q), c_int(q.stride(0)), _ptr(k), c_int(k.stride(0)), c_int(heads_per_qk), _ptr(decay_vec),
+        c_int(decay_vec.stride(0) if decay_vec is not None else 0), _ptr(v), c_int(v.stride(0)),
         _ptr(dt_dec), _ptr(decay_head), _ptr(skip), _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(out),
         _ptr(seq_slot), _ptr(seq_q_start), _ptr(seq_q_len), c_int(n_seqs), c_int(T), c_int(heads), c_int(dim), c_int(vdim),
         c_int(1 if write_state else 0), _stream()), "decay_walk")
+
+
+def gla_gates(proj: torch.Tensor, low_off: int, rank: int, a2t: torch.Tensor, bias: torch.Tensor | None, tau: float,
+              f_out: torch.Tensor, q_off: int, q_cols: int, q_scale: float, defines: dict) -> None:
+    """Decays of gated linear attention from float32 projections [T, .]: f = sigmoid(low @ a2t + bias)^(1 / tau) with
+    low = proj[:, low_off : low_off + rank] and a2t float32 [rank, C]; f_out float32 [T, C].  Also scales the ``q_cols``
+    columns at ``q_off`` by ``q_scale``, in place."""
+    _need_cuda(proj, a2t, bias, f_out)
+    T = proj.shape[0]
+    C = a2t.shape[1]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= max(low_off + rank, q_off + q_cols),
+          "gla_gates: float32 projections")
+    _need(a2t.dtype == torch.float32 and a2t.is_contiguous() and a2t.shape[0] == rank, "gla_gates: a2t float32 [rank, C]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C), "gla_gates: bias float32 [C]")
+    _need(f_out.dtype == torch.float32 and f_out.is_contiguous() and tuple(f_out.shape) == (T, C) and tau > 0, "gla_gates: f_out, tau")
+    _check(_fn(_libs.get("decay_recurrence.cu", **defines), "tkb_gla_gates")(
+        _ptr(proj), c_int(proj.stride(0)), c_int(low_off), c_int(rank), _ptr(a2t), _ptr(bias), c_float(1.0 / tau), c_int(C),
+        _ptr(f_out), c_int(q_off), c_int(q_cols), c_float(q_scale), c_int(T), _stream()), "gla_gates")
+
+
+def rotate_scale(proj: torch.Tensor, q_off: int, k_off: int, heads: int, dim: int, rot_dims: int, pairs: bool,
+                 freq: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor, q_scale: float, k_scale: float,
+                 defines: dict) -> None:
+    """Rotation by position of the ``heads`` q heads (at column ``q_off``) and k heads (at ``k_off``) of float32 rows,
+    in place, on the first ``rot_dims`` channels of a head (``pairs``: channel 2i with 2i + 1, else i with
+    i + rot_dims / 2; freq float64 [rot_dims / 2]), then q * q_scale and k * k_scale."""
+    _need_cuda(proj, freq, positions, token_seq)
+    T = proj.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= max(q_off, k_off) + heads * dim,
+          "rotate_scale: float32 projections")
+    _need(0 <= rot_dims <= dim and rot_dims % 2 == 0 and freq.dtype == torch.float64 and freq.is_contiguous()
+          and freq.numel() == rot_dims // 2, "rotate_scale: float64 [rot_dims / 2] frequencies")
+    _need(positions.dtype == torch.int32 and positions.numel() >= T and token_seq.numel() >= T, "rotate_scale: positions")
+    _check(_fn(_libs.get("decay_recurrence.cu", **defines), "tkb_rotate_scale")(
+        _ptr(proj), c_int(proj.stride(0)), c_int(q_off), c_int(k_off), c_int(heads), c_int(dim), c_int(rot_dims),
+        c_int(1 if pairs else 0), _ptr(freq), _ptr(positions), _ptr(token_seq), c_float(q_scale), c_float(k_scale),
+        c_int(T), _stream()), "rotate_scale")
 
 
 def silu_cols(x: torch.Tensor, ncols: int, defines: dict) -> None:
@@ -1200,44 +1310,70 @@ def silu_cols(x: torch.Tensor, ncols: int, defines: dict) -> None:
 
 # ---------------------------------------------------------------------------------------------
 # Attention with a score cap and a sink, keys and values of different sizes (csrc/attention_sink.cu)
-def sink_attention_defines(dim: int, vdim: int) -> dict:
+def sink_attention_defines(dim: int, vdim: int, sigmoid: bool = False) -> dict:
+    """``sigmoid``: the build whose weights are sigmoid(score), not a softmax."""
     _need(0 < dim <= 512 and 0 < vdim <= 512, f"sink attention: head sizes up to 512, not {dim} / {vdim}")
-    return dict(TKB_QK=dim, TKB_VD=vdim)
+    return dict(TKB_QK=dim, TKB_VD=vdim, TKB_SIGMOID=1) if sigmoid else dict(TKB_QK=dim, TKB_VD=vdim)
 
 
 def sink_attn_prep(qkv: torch.Tensor, bias: torch.Tensor | None, unit_norm: bool, eps: float, q_out: torch.Tensor,
                    cache: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor, page_indptr: torch.Tensor,
                    page_ids: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int,
-                   write_cache: bool, status: torch.Tensor) -> None:
+                   write_cache: bool, status: torch.Tensor, norm_w: torch.Tensor | None = None,
+                   rot_freq: torch.Tensor | None = None, rot_dims: int = 0, rot_pairs: bool = False,
+                   values_are_keys: bool = False, sigmoid: bool = False) -> None:
     """qkv float32 [T, heads*dim | kv heads*dim | kv heads*vdim] -> (+ bias, q and k heads divided by their root mean
-    square) q_out [T, heads*dim] and the tokens' [k | v] rows in cache [pages, kv heads, page_size, dim + vdim]."""
-    _need_cuda(qkv, bias, q_out, cache, positions, token_seq, page_indptr, page_ids, status)
+    square) q_out [T, heads*dim] and the tokens' [k | v] rows in cache [pages, kv heads, page_size, dim + vdim].
+    ``norm_w`` float32 [2, dim]: weights of the q heads' and the k heads' norm.  ``rot_freq`` float64 [rot_dims / 2]:
+    q and k are rotated by position on their first ``rot_dims`` channels (``rot_pairs``: channel 2i with 2i + 1, else
+    i with i + rot_dims / 2).  ``values_are_keys``: the projections hold no v; a token's value is its key as projected
+    (before norm and rotation).  ``sigmoid``: the kernel build of the sigmoid form."""
+    _need_cuda(qkv, bias, q_out, cache, positions, token_seq, page_indptr, page_ids, status, norm_w, rot_freq)
     T = qkv.shape[0]
-    C = (n_heads + n_kv_heads) * dim + n_kv_heads * vdim
+    C = (n_heads + n_kv_heads) * dim + (0 if values_are_keys else n_kv_heads * vdim)
+    _need(not values_are_keys or dim == vdim, "sink_attn_prep: values that are the keys have the keys' size")
+    _need(norm_w is None or (norm_w.dtype == torch.float32 and norm_w.is_contiguous() and tuple(norm_w.shape) == (2, dim)),
+          "sink_attn_prep: norm weights float32 [2, dim]")
+    _need(rot_freq is None or (rot_freq.dtype == torch.float64 and rot_freq.is_contiguous() and rot_dims % 2 == 0
+                               and 0 < rot_dims <= dim and rot_freq.numel() == rot_dims // 2),
+          "sink_attn_prep: float64 [rot_dims / 2] frequencies")
     _need(qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] == C, "sink_attn_prep: float32 projections")
     _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C), "sink_attn_prep: bias float32")
     _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, n_heads * dim) and q_out.dtype == cache.dtype, "sink_attn_prep: q_out")
     _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, dim + vdim), "sink_attn_prep: cache rows")
-    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim)), f"tkb_sink_attn_prep_{_suffix(cache.dtype)}")(
+    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, sigmoid)), f"tkb_sink_attn_prep_{_suffix(cache.dtype)}")(
         _ptr(qkv), c_int(qkv.stride(0)), _ptr(bias), c_int(1 if unit_norm else 0), c_float(eps), _ptr(q_out), _ptr(cache),
         _ptr(positions), _ptr(token_seq), _ptr(page_indptr), _ptr(page_ids), c_int(T), c_int(n_heads), c_int(n_kv_heads),
-        c_int(page_size), c_int(cache.shape[0]), c_int(1 if write_cache else 0), _ptr(status), _stream()), "sink_attn_prep")
+        c_int(page_size), c_int(cache.shape[0]), c_int(1 if write_cache else 0), _ptr(status), _ptr(norm_w), _ptr(rot_freq),
+        c_int(rot_dims if rot_freq is not None else 0), c_int(1 if rot_pairs else 0), c_int(1 if values_are_keys else 0),
+        _stream()), "sink_attn_prep")
+
+
+def _head_vectors(n_heads: int, what: str, *vectors):
+    for v in vectors:
+        _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == n_heads), f"{what}: float32 [heads] vectors")
 
 
 def attn_sink(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
               page_indptr: torch.Tensor, page_ids: torch.Tensor, rows: torch.Tensor | None, n_rows: int,
               sinks: torch.Tensor | None, n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int,
-              scale: float, softcap: float | None, window: int | None, status: torch.Tensor) -> None:
-    """Attention of ``n_rows`` tokens (``rows`` names them; None: all) over their requests' cached [k | v] rows."""
-    _need_cuda(q, out, cache, token_seq, positions, page_indptr, page_ids, rows, sinks, status)
+              scale: float, softcap: float | None, window: int | None, status: torch.Tensor,
+              head_scale: torch.Tensor | None = None, head_bias: torch.Tensor | None = None, sigmoid: bool = False) -> None:
+    """Attention of ``n_rows`` tokens (``rows`` names them; None: all) over their requests' cached [k | v] rows.
+    ``head_scale`` / ``head_bias`` float32 [heads]: a factor on a head's scale, a number added to its scores.
+    ``sigmoid``: weights sigmoid(score) instead of a softmax (no sink)."""
+    _need_cuda(q, out, cache, token_seq, positions, page_indptr, page_ids, rows, sinks, status, head_scale, head_bias)
+    _head_vectors(n_heads, "attn_sink", head_scale, head_bias)
+    _need(not (sigmoid and sinks is not None), "attn_sink: the sigmoid form has no sink")
     _need(q.is_contiguous() and q.shape[1] == n_heads * dim and q.dtype == cache.dtype and out.dtype == cache.dtype
           and out.is_contiguous() and tuple(out.shape) == (n_rows, n_heads * vdim), "attn_sink: q and out")
     _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, dim + vdim), "attn_sink: cache rows")
     _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads), "attn_sink: sinks float32 [heads]")
-    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim)), f"tkb_attn_sink_simt_{_suffix(cache.dtype)}")(
+    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, sigmoid)), f"tkb_attn_sink_simt_{_suffix(cache.dtype)}")(
         _ptr(q), _ptr(out), _ptr(cache), _ptr(token_seq), _ptr(positions), _ptr(page_indptr), _ptr(page_ids), _ptr(rows),
         c_int(n_rows), _ptr(sinks), c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale),
-        c_float(softcap or 0.0), c_int(window or 0), c_int(cache.shape[0]), _ptr(status), _stream()), "attn_sink")
+        c_float(softcap or 0.0), c_int(window or 0), c_int(cache.shape[0]), _ptr(status), _ptr(head_scale), _ptr(head_bias),
+        _stream()), "attn_sink")
 
 
 def can_use_attn_sink_tc(dtype: torch.dtype, dim: int, vdim: int) -> bool:
@@ -1250,10 +1386,13 @@ def attn_sink_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, seq_q_
                  seq_kv_len: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor, n_seqs: int,
                  sinks: torch.Tensor | None, n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int, scale: float,
                  softcap: float | None, window: int | None, status: torch.Tensor, portions: bool = True,
-                 singles: bool = True) -> None:
+                 singles: bool = True, head_scale: torch.Tensor | None = None, head_bias: torch.Tensor | None = None,
+                 sigmoid: bool = False) -> None:
     """Attention of every token of the step on the tensor cores (bfloat16): out [T, heads * vdim].  ``portions`` /
     ``singles``: whether the step can hold requests with several tokens / with one (a kernel each)."""
-    _need_cuda(q, out, cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, sinks, status)
+    _need_cuda(q, out, cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, sinks, status, head_scale, head_bias)
+    _head_vectors(n_heads, "attn_sink_tc", head_scale, head_bias)
+    _need(not (sigmoid and sinks is not None), "attn_sink_tc: the sigmoid form has no sink")
     T = q.shape[0]
     _need(can_use_attn_sink_tc(cache.dtype, dim, vdim), "attn_sink_tc: bfloat16 rows, key and value sizes multiples of 16")
     _need(q.is_contiguous() and q.shape[1] == n_heads * dim and q.dtype == cache.dtype and out.dtype == cache.dtype
@@ -1272,11 +1411,12 @@ def attn_sink_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, seq_q_
             splits = min(splits, max(1, (window + 63) // 64))
         if splits > 1:
             part = torch.empty((n_seqs * n_heads * splits * (vdim + 2),), dtype=torch.float32, device=q.device)
-    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim)), "tkb_attn_sink_tc_bf16")(
+    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, sigmoid)), "tkb_attn_sink_tc_bf16")(
         _ptr(q), _ptr(out), _ptr(cache), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(page_indptr),
         _ptr(page_ids), c_int(T), c_int(n_seqs), c_int(1 if portions else 0), c_int(1 if singles else 0), _ptr(sinks),
         c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_float(softcap or 0.0), c_int(window or 0),
-        c_int(cache.shape[0]), _ptr(status), _ptr(part), c_int(splits), _stream()), "attn_sink_tc")
+        c_int(cache.shape[0]), _ptr(status), _ptr(part), c_int(splits), _ptr(head_scale), _ptr(head_bias), _stream()),
+        "attn_sink_tc")
 
 
 def prepare_modules(modules) -> None:

@@ -31,7 +31,7 @@ class WeightSpec:
     """One tensor a part reads from the weight files, by its name there."""
 
     name: str
-    shape: tuple[int, ...]
+    shape: tuple[int, ...]  # a size of -1: whatever the file holds (a size that no configuration key gives)
     # "matrix": cast to the engine's dtype.  "vector": small per-channel tensor used in
     # 32-bit arithmetic (norm weights); always held as float32.  "table": integer table,
     # held as int32.

@@ -153,3 +153,58 @@ class OutputNormBlock(Part):
         if self.ffn is not None:
             self._add(stream, self.ffn.forward(ctx, self._input(stream)), self.ffn_norm, self.scales[1])
         return stream
+
+
+class PostNormBlock(Part):
+    """A block that norms AFTER each residual sum, with the stream scaled on its way into the sum:
+
+        x <- norm1(alpha * x + mixer(x)),      x <- norm2(alpha * x + ffn(x)),      x <- side(x)  (optional)
+
+    The sublayers read x itself.  The norms are ``parts.norm.GroupRMSNorm`` (RMS norm in equal parts of a row, one
+    weight vector); ``side`` is a part that adds a per-token input to the stream after the feed-forward
+    (``parts.side_input.TokenSideInput``).  The stream stays float32: the kernel that norms a sum writes the new stream
+    in both types, a sublayer's output arrives as float32 rows, as the float32 slices of a K-split product (few rows),
+    or in the activation type.  A block without a feed-forward has no second sum and no second norm."""
+
+    def __init__(self, mixer: Mixer, mixer_norm, ffn: FeedForward | None, ffn_norm, alpha: float = 1.0, side=None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a block has a feed-forward and its norm, or neither")
+        self.mixer, self.mixer_norm, self.ffn, self.ffn_norm, self.side = mixer, mixer_norm, ffn, ffn_norm, side
+        self.alpha = float(alpha)
+        self.dtype: torch.dtype | None = None
+
+    def parts(self):
+        return tuple(p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm, self.side) if p is not None)
+
+    def weight_specs(self):
+        return tuple(s for p in self.parts() for s in p.weight_specs())
+
+    def kernel_modules(self, dtype):
+        return (("post_norm.cu", None),) + tuple(m for p in self.parts() for m in p.kernel_modules(dtype))
+
+    def bind(self, weights, rt) -> None:
+        for p in self.parts():
+            p.bind(weights, rt)
+        self.dtype = rt.dtype
+
+    def state_needs(self) -> dict:
+        return {}
+
+    def _input(self, stream: ResidualStream) -> torch.Tensor:
+        if self.dtype == torch.float32:
+            return stream.x
+        if stream.h is None:
+            stream.h = torch.empty(stream.x.shape, dtype=self.dtype, device=stream.x.device)
+            ops.cast_rows(stream.x, stream.h)
+        return stream.h
+
+    def forward(self, ctx, stream: ResidualStream, cache, out_rows=None, stage_state=None) -> ResidualStream:
+        y = self.mixer.forward(ctx, self._input(stream), cache, out_rows)
+        if out_rows is not None:
+            stream = PreNormBlock._cut(stream, out_rows)
+        stream.h = self.mixer_norm.apply_sum(stream.x, y, self.alpha)
+        if self.ffn is not None:
+            stream.h = self.ffn_norm.apply_sum(stream.x, self.ffn.forward(ctx, self._input(stream)), self.alpha)
+        if self.side is not None:
+            self.side.forward(ctx, stream, self._input(stream), out_rows)
+        return stream

@@ -135,7 +135,14 @@ class RoutedExperts(FeedForward):
     weighted sum of their outputs, plus a shared expert (any ``FeedForward``) that every token runs through.
 
     A step's (token, choice) pairs are ordered by expert on the device, and the experts' products run over that
-    ordering with each block looking its expert up; nothing about the routing is read back to the host."""
+    ordering with each block looking its expert up; nothing about the routing is read back to the host.
+
+    ``scored`` = dict(correction=<tensor name or None>, groups, keep, scale): the other way of choosing.  Scores
+    s = sigmoid(logits); the choice goes by s + correction (a learned vector that takes no part in the weights), among
+    the experts of the best ``keep`` of ``groups`` equal groups of neighbours only (a group scores the sum of its two
+    largest choice scores); the weights are the chosen experts' s over their sum, times ``scale``.
+    ``expert="gelu"``: an expert is ``down(gelu(up h))`` with the exact GELU and no gate; ``expert_names(e)`` then gives
+    (up, down).  ``out_dtype`` float32: the weighted sum leaves as float32 rows (for a norm that reads it)."""
 
     # (token, choice) pairs from which the gathered tcgen05 products are used (bfloat16).  Below, the few-rows kernel
     # fetches every chosen expert's weights once as well, but spends one multiply-add a row on every weight it
@@ -145,10 +152,18 @@ class RoutedExperts(FeedForward):
     TENSOR_CORE_PAIRS_MIN = 12
 
     def __init__(self, width: int, inner: int, n_experts: int, top: int, router_name: str, router_bias_name: str | None,
-                 expert_names, shared: FeedForward | None = None):
+                 expert_names, shared: FeedForward | None = None, scored: dict | None = None, expert: str = "silu_gated",
+                 out_dtype: torch.dtype | None = None):
         """``expert_names(e)`` -> (gate, up, down) tensor names of expert e."""
         if not 0 < top <= n_experts:
             raise ValueError(f"top={top} of {n_experts} experts")
+        if expert not in ("silu_gated", "gelu"):
+            raise ValueError(f"an expert is 'silu_gated' or 'gelu', not {expert!r}")
+        if scored is not None:
+            g, keep = int(scored.get("groups", 1)), int(scored.get("keep", 1))
+            if g <= 0 or n_experts % g or not 0 < keep <= g or top > keep * (n_experts // g):
+                raise ValueError(f"{n_experts} experts in {g} groups of which {keep} are kept, {top} chosen")
+        self.scored, self.gelu, self.out_dtype = scored, expert == "gelu", out_dtype
         self.width, self.inner, self.n_experts, self.top = width, inner, n_experts, top
         self.router_name, self.router_bias_name = router_name, router_bias_name
         self.expert_names = [tuple(expert_names(e)) for e in range(n_experts)]
@@ -158,9 +173,10 @@ class RoutedExperts(FeedForward):
         specs = [WeightSpec(self.router_name, (self.n_experts, self.width), role="vector")]
         if self.router_bias_name is not None:
             specs.append(WeightSpec(self.router_bias_name, (self.n_experts,), role="vector"))
-        for g, u, d in self.expert_names:
-            specs += [WeightSpec(g, (self.inner, self.width)), WeightSpec(u, (self.inner, self.width)),
-                      WeightSpec(d, (self.width, self.inner))]
+        if self.scored is not None and self.scored.get("correction") is not None:
+            specs.append(WeightSpec(self.scored["correction"], (self.n_experts,), role="vector"))
+        for names in self.expert_names:
+            specs += [WeightSpec(n, (self.inner, self.width)) for n in names[:-1]] + [WeightSpec(names[-1], (self.width, self.inner))]
         if self.shared is not None:
             specs += list(self.shared.weight_specs())
         return tuple(specs)
@@ -172,16 +188,23 @@ class RoutedExperts(FeedForward):
     def bind(self, weights, rt) -> None:
         self.router_w = weights[self.router_name].contiguous()
         self.router_b = weights[self.router_bias_name].contiguous() if self.router_bias_name is not None else None
-        # [E, 2 * inner, width]: each expert's gate rows, then its up rows;  [E, width, inner]
-        self.w_gate_up = torch.stack([torch.cat([weights[g], weights[u]], dim=0) for g, u, _ in self.expert_names]).contiguous()
-        self.w_down = torch.stack([weights[d] for _, _, d in self.expert_names]).contiguous()
+        self.route_args = None
+        if self.scored is not None:
+            c = self.scored.get("correction")
+            self.route_args = dict(correction=weights[c].contiguous() if c is not None else None,
+                                   groups=int(self.scored.get("groups", 1)), keep=int(self.scored.get("keep", 1)),
+                                   scale=float(self.scored.get("scale", 1.0)))
+        # [E, 2 * inner, width]: each expert's gate rows, then its up rows ([E, inner, width]: the up rows of an
+        # ungated expert);  [E, width, inner]
+        self.w_gate_up = torch.stack([torch.cat([weights[n] for n in names[:-1]], dim=0) for names in self.expert_names]).contiguous()
+        self.w_down = torch.stack([weights[names[-1]] for names in self.expert_names]).contiguous()
         # for steps of many rows in bfloat16: the same weights with every expert's gate and up rows interleaved in
         # groups of 8, the layout whose product the tcgen05 kernel turns into silu(gate) * up in its epilogue
         self.w_gate_up_tc = None
         # (sizes below one tile of the kernel's TMA boxes stay with the other kernels)
         if rt.dtype == torch.bfloat16 and self.inner % 8 == 0 and self.width % 8 == 0 and self.inner >= 64 and self.width >= 128:
-            self.w_gate_up_tc = torch.stack([ops.interleave_gate_up(weights[g], weights[u])
-                                             for g, u, _ in self.expert_names]).contiguous()
+            self.w_gate_up_tc = self.w_gate_up if self.gelu else torch.stack(
+                [ops.interleave_gate_up(weights[g], weights[u]) for g, u, _ in self.expert_names]).contiguous()
         if self.shared is not None:
             self.shared.bind(weights, rt)
 
@@ -192,11 +215,11 @@ class RoutedExperts(FeedForward):
         top_w = torch.empty((T, top), dtype=torch.float32, device=dev)
         # rows of padding tokens (a step graph's) choose nothing; a cut-down set of rows has none
         token_seq = ctx.token_seq if (ctx is not None and T == ctx.n_tokens) else None
-        ops.moe_route(h, self.router_w, self.router_b, token_seq, top, top_idx, top_w)
+        ops.moe_route(h, self.router_w, self.router_b, token_seq, top, top_idx, top_w, self.route_args)
         offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
         place_of = torch.empty((T * top,), dtype=torch.int32, device=dev)
         shared = self.shared.forward(ctx, h) if self.shared is not None else None
-        out = torch.empty((T, self.width), dtype=h.dtype, device=dev)
+        out = torch.empty((T, self.width), dtype=self.out_dtype or h.dtype, device=dev)
         if self.w_gate_up_tc is not None and T * top >= self.TENSOR_CORE_PAIRS_MIN:
             # many rows: the rows gathered expert by expert, every span on a 128-row tile boundary, and the two
             # products on the tcgen05 tensor cores, each row tile with its own expert's weights
@@ -209,14 +232,14 @@ class RoutedExperts(FeedForward):
             rows = torch.empty((n_tiles * tile, self.width), dtype=h.dtype, device=dev)
             ops.moe_gather(h, src_token, rows)
             status = ctx.status if ctx is not None else torch.zeros(1, dtype=torch.int32, device=dev)
-            act = ops.gemm_tcgen05_grouped(rows, self.w_gate_up_tc, tile_group, status, gated=True)
+            act = ops.gemm_tcgen05_grouped(rows, self.w_gate_up_tc, tile_group, status, gated=not self.gelu, gelu=self.gelu)
             y = ops.gemm_tcgen05_grouped(act, self.w_down, tile_group, status)
             ops.moe_combine(y, place_of, top_w, shared, out)
             return out
         order = torch.empty((T * top,), dtype=torch.int32, device=dev)
         ops.moe_order(top_idx, E, offsets, order, place_of)
         act = torch.empty((T * top, self.inner), dtype=h.dtype, device=dev)
-        ops.moe_gemm(h, self.w_gate_up, act, offsets, order, top, gated=True)
+        ops.moe_gemm(h, self.w_gate_up, act, offsets, order, top, gated=not self.gelu, gelu=self.gelu)
         y = torch.empty((T * top, self.width), dtype=torch.float32, device=dev)
         ops.moe_gemm(act, self.w_down, y, offsets, None, top, gated=False)
         ops.moe_combine(y, place_of, top_w, shared, out)

@@ -36,6 +36,42 @@ class RMSNorm(Norm):
         return out
 
 
+class GroupRMSNorm(Norm):
+    """RMS norm in equal consecutive parts of a row: every part is divided by its own ``sqrt(mean(part^2) + eps)``, then
+    the whole row is multiplied by one weight vector.  ``groups`` = 1 is the plain RMS norm.  Blocks that norm AFTER the
+    residual sum (``parts.block.PostNormBlock``) hand their sum to the same kernel; ``forward`` serves an output head."""
+
+    def __init__(self, width: int, eps: float, weight_name: str, groups: int = 1):
+        if groups <= 0 or width % groups:
+            raise ValueError(f"a row of {width} values does not divide into {groups} equal parts")
+        self.width, self.eps, self.weight_name, self.groups = width, float(eps), weight_name, int(groups)
+        self.weight: torch.Tensor | None = None
+        self.out_dtype: torch.dtype | None = None
+
+    def weight_specs(self):
+        return (WeightSpec(self.weight_name, (self.width,), role="vector"),)
+
+    def kernel_modules(self, dtype):
+        return (("post_norm.cu", None),)
+
+    def bind(self, weights, rt) -> None:
+        self.weight = weights[self.weight_name]
+        self.out_dtype = rt.dtype
+
+    def apply_sum(self, x: torch.Tensor, y, alpha: float) -> torch.Tensor | None:
+        """x = weight * N(alpha * x + y) in place on the float32 rows ``x``; returns the new rows in the activation type
+        (None in a float32 engine: they are ``x`` itself)."""
+        h = None if self.out_dtype == torch.float32 else torch.empty(x.shape, dtype=self.out_dtype, device=x.device)
+        ops.sum_group_norm(x, y, alpha, self.weight, self.eps, self.groups, h)
+        return h
+
+    def forward(self, ctx, stream: ResidualStream):
+        # (the stream ends here: norming it in place costs no copy)
+        h = self.apply_sum(stream.x, stream.delta, 1.0)
+        stream.delta = None
+        return stream.x if h is None else h
+
+
 class LayerNorm(Norm):
     """``y = (x - mean) / sqrt(var + eps) * weight + bias`` with ``var = mean((x - mean)^2)``, statistics in float32;
     the kernel folds the residual add in like ``RMSNorm``'s."""

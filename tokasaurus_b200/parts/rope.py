@@ -50,6 +50,14 @@ class RotaryEncoding(PositionEncoding):
         self.high_freq_factor = float(high_freq_factor)
         self.original_max_position_embeddings = int(original_max_position_embeddings)
 
+    def inv_freq64(self) -> torch.Tensor:
+        """float64 [rotary_dim / 2] ``theta^(-2j / rotary_dim)``, on the CPU, for kernels that form their angles in
+        float64 (plain frequencies only)."""
+        if self.scaling_type != "default":
+            raise ValueError("float64 frequencies exist for the plain rotary encoding")
+        d = self.rotary_dim
+        return self.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
+
     def inv_freq(self) -> torch.Tensor:
         """float32 [rotary_dim / 2], on the CPU."""
         d = self.rotary_dim

@@ -14,6 +14,13 @@ A token's key and value of one key/value head are cached side by side as one row
 scores, weights and sums are float32.  In float32, and for head sizes that are no multiples of 16, one FP32-pipe kernel
 serves every token; in bfloat16 otherwise the tensor-core kernels of csrc/attention_sink.cu do (weights rounded to
 bfloat16 for their product with the values, as in the framework's other attention kernels).
+
+Options that other designs bring: a weight vector on the q and k norms (``qk_norm_names``); a rotation of q and k by
+position on the first ``rotary.rotary_dim`` channels of a head, in neighbouring pairs or in halves (``rotary``,
+``rotary_pairs``; after the norm); values that ARE the keys as projected, before norm and rotation
+(``values_are_keys``: no W_v, vdim = dim); a learned factor on every head's scale and a learned number added to its
+scores (``head_scale_name``, ``head_bias_name``); and ``weights="sigmoid"``: no softmax, the weight of a visible key
+is sigmoid(score), not normalised over the keys (then there is no sink).
 """
 
 from __future__ import annotations
@@ -30,9 +37,26 @@ class SinkAttention(Mixer):
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
                  softcap: float | None, window: int | None, norm_eps: float, q_name: str, k_name: str, v_name: str,
                  o_name: str, sink_name: str | None, bias_names: tuple[str, str, str] | None = None,
-                 out_bias_name: str | None = None, unit_norm: bool = True):
+                 out_bias_name: str | None = None, unit_norm: bool = True, qk_norm_names: tuple[str, str] | None = None,
+                 rotary=None, rotary_pairs: bool = True, values_are_keys: bool = False,
+                 head_scale_name: str | None = None, head_bias_name: str | None = None, weights: str = "softmax"):
         if n_heads % n_kv_heads:
             raise ValueError(f"n_heads={n_heads} is not a multiple of n_kv_heads={n_kv_heads}")
+        if weights not in ("softmax", "sigmoid"):
+            raise ValueError(f"attention weights are 'softmax' or 'sigmoid', not {weights!r}")
+        if weights == "sigmoid" and sink_name is not None:
+            raise ValueError("sigmoid weights are not normalised: there is no sink")
+        if values_are_keys and vdim != dim:
+            raise ValueError(f"values that are the keys have the keys' size {dim}, not {vdim}")
+        if qk_norm_names is not None and not unit_norm:
+            raise ValueError("norm weights need the norm")
+        if rotary is not None and rotary.rotary_dim > dim:
+            raise ValueError(f"{rotary.rotary_dim} rotated channels in heads of {dim}")
+        self.sigmoid = weights == "sigmoid"
+        self.qk_norm_names, self.rotary, self.rotary_pairs = qk_norm_names, rotary, bool(rotary_pairs)
+        self.values_are_keys = bool(values_are_keys)
+        self.head_scale_name, self.head_bias_name = head_scale_name, head_bias_name
+        self.qk_norm_w = self.rot_freq = self.head_scale = self.head_bias = None
         self.width, self.n_heads, self.n_kv_heads, self.dim, self.vdim = width, n_heads, n_kv_heads, dim, vdim
         self.scale = float(scale)
         self.softcap = float(softcap) if softcap else None
@@ -40,16 +64,21 @@ class SinkAttention(Mixer):
         self.norm_eps, self.unit_norm = float(norm_eps), bool(unit_norm)
         self.names = (q_name, k_name, v_name, o_name)
         self.sink_name, self.bias_names, self.out_bias_name = sink_name, bias_names, out_bias_name
-        self.defines = ops.sink_attention_defines(dim, vdim)
+        self.defines = ops.sink_attention_defines(dim, vdim, self.sigmoid)
         self.sinks = self.qkv_bias = self.out_bias = None
 
     def weight_specs(self):
         q, k, v, o = self.names
         H, G, d, e = self.n_heads, self.n_kv_heads, self.dim, self.vdim
-        specs = [WeightSpec(q, (H * d, self.width)), WeightSpec(k, (G * d, self.width)),
-                 WeightSpec(v, (G * e, self.width)), WeightSpec(o, (self.width, H * e))]
+        specs = [WeightSpec(q, (H * d, self.width)), WeightSpec(k, (G * d, self.width)), WeightSpec(o, (self.width, H * e))]
+        if not self.values_are_keys:
+            specs.append(WeightSpec(v, (G * e, self.width)))
+        if self.qk_norm_names is not None:
+            specs += [WeightSpec(n, (d,), role="vector") for n in self.qk_norm_names]
+        specs += [WeightSpec(n, (H,), role="vector") for n in (self.head_scale_name, self.head_bias_name) if n is not None]
         if self.bias_names is not None:
-            specs += [WeightSpec(n, (rows,), role="vector") for n, rows in zip(self.bias_names, (H * d, G * d, G * e))]
+            specs += [WeightSpec(n, (rows,), role="vector")
+                      for n, rows in zip(self.bias_names, (H * d, G * d) if self.values_are_keys else (H * d, G * d, G * e))]
         if self.out_bias_name is not None:
             specs.append(WeightSpec(self.out_bias_name, (self.width,), role="vector"))
         if self.sink_name is not None:
@@ -64,10 +93,19 @@ class SinkAttention(Mixer):
 
     def bind(self, weights, rt) -> None:
         q, k, v, o = self.names
-        self.w_qkv = torch.cat([weights[q], weights[k], weights[v]], dim=0).contiguous()
+        self.w_qkv = torch.cat([weights[q], weights[k]] + ([] if self.values_are_keys else [weights[v]]), dim=0).contiguous()
         self.w_o = weights[o].contiguous()
         if self.bias_names is not None:
-            self.qkv_bias = torch.cat([weights[n].float() for n in self.bias_names]).contiguous()
+            names = self.bias_names[:2] if self.values_are_keys else self.bias_names
+            self.qkv_bias = torch.cat([weights[n].float() for n in names]).contiguous()
+        if self.qk_norm_names is not None:
+            self.qk_norm_w = torch.stack([weights[n].float() for n in self.qk_norm_names]).contiguous()
+        if self.rotary is not None and self.rotary.rotary_dim > 0:
+            self.rot_freq = self.rotary.inv_freq64().to(rt.device)
+        if self.head_scale_name is not None:
+            self.head_scale = weights[self.head_scale_name].contiguous()
+        if self.head_bias_name is not None:
+            self.head_bias = weights[self.head_bias_name].contiguous()
         if self.out_bias_name is not None:
             self.out_bias = weights[self.out_bias_name].contiguous()
         if self.sink_name is not None:
@@ -80,14 +118,18 @@ class SinkAttention(Mixer):
         qkv = ops.linear(h, self.w_qkv, out_dtype=torch.float32)
         q = torch.empty((T, H * d), dtype=h.dtype, device=h.device)
         ops.sink_attn_prep(qkv, self.qkv_bias, self.unit_norm, self.norm_eps, q, cache.k, ctx.positions, ctx.token_seq,
-                           tables.indptr, tables.page_ids, H, G, d, e, cache.page_size, cache.writable, ctx.status)
+                           tables.indptr, tables.page_ids, H, G, d, e, cache.page_size, cache.writable, ctx.status,
+                           norm_w=self.qk_norm_w, rot_freq=self.rot_freq,
+                           rot_dims=self.rotary.rotary_dim if self.rot_freq is not None else 0,
+                           rot_pairs=self.rotary_pairs, values_are_keys=self.values_are_keys, sigmoid=self.sigmoid)
         if ops.can_use_attn_sink_tc(h.dtype, d, e):
             # bfloat16: every token on the tensor cores (single tokens and portions by a kernel each); wanted rows are
             # cut out afterwards
             attn = torch.empty((T, H * e), dtype=h.dtype, device=h.device)
             ops.attn_sink_tc(q, attn, cache.k, ctx.seq_q_start, ctx.seq_q_len, ctx.seq_kv_len, tables.indptr,
                              tables.page_ids, ctx.n_seqs, self.sinks, H, G, d, e, cache.page_size, self.scale, self.softcap,
-                             self.window, ctx.status, portions=not ctx.single_token_step)
+                             self.window, ctx.status, portions=not ctx.single_token_step, head_scale=self.head_scale,
+                             head_bias=self.head_bias, sigmoid=self.sigmoid)
             if out_rows is not None:
                 cut = torch.empty((out_rows.numel(), H * e), dtype=h.dtype, device=h.device)
                 ops.gather_rows(attn, out_rows, cut)
@@ -96,5 +138,6 @@ class SinkAttention(Mixer):
         n_rows = T if out_rows is None else out_rows.numel()
         attn = torch.empty((n_rows, H * e), dtype=h.dtype, device=h.device)
         ops.attn_sink(q, attn, cache.k, ctx.token_seq, ctx.positions, tables.indptr, tables.page_ids, out_rows, n_rows,
-                      self.sinks, H, G, d, e, cache.page_size, self.scale, self.softcap, self.window, ctx.status)
+                      self.sinks, H, G, d, e, cache.page_size, self.scale, self.softcap, self.window, ctx.status,
+                      head_scale=self.head_scale, head_bias=self.head_bias, sigmoid=self.sigmoid)
         return ops.linear_out_f32(attn, self.w_o, ctx.status)

@@ -105,7 +105,9 @@ def load_weights(folder: str | Path, specs: Iterable[WeightSpec], engine_dtype: 
         with safe_open(str(path), framework="pt") as f:
             for n in names:
                 shape = tuple(f.get_slice(n).get_shape())
-                if shape != tuple(wanted[n].shape):
+                want = tuple(wanted[n].shape)
+                # (a wanted size of -1 is one that only the file knows: the part reads it from the tensor it is given)
+                if len(shape) != len(want) or any(w >= 0 and w != g for g, w in zip(shape, want)):
                     wrong.append((n, shape, tuple(wanted[n].shape)))
                     continue
                 if missing or unexpected or wrong or other:

@@ -35,6 +35,8 @@ def random_tensors(specs: Iterable[WeightSpec], seed: int, std: float = 0.02, no
     g.manual_seed(int(seed))
     out: dict[str, torch.Tensor] = {}
     for s in specs:
+        if any(d < 0 for d in s.shape):  # a size that only a weight file knows: random weights take 16
+            s = WeightSpec(s.name, tuple(16 if d < 0 else d for d in s.shape), s.role, s.keep_32bit)
         if s.role == "table":
             out[s.name] = torch.randint(0, 2**15, s.shape, generator=g, dtype=torch.int32, device=device)
         elif s.role == "vector":
