@@ -27,6 +27,34 @@ import torch
 
 F64 = torch.float64
 
+# When set (``rounded``), every matrix product's left operand is passed through it first: rounding the rows to 16 bits
+# and back shows how far a 16-bit engine's rounding alone moves the logits at each position.
+_ROUND = None
+
+
+class rounded:
+    """``with rounded(fn): forward(...)``: the inputs of all matrix products go through ``fn``."""
+
+    def __init__(self, fn):
+        self.fn = fn
+
+    def __enter__(self):
+        global _ROUND
+        self.before, _ROUND = _ROUND, self.fn
+
+    def __exit__(self, *exc):
+        global _ROUND
+        _ROUND = self.before
+
+
+def to_bfloat16_and_back(x):
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
+def lin(x, w):
+    """W x for every row of x; W is [out, in]."""
+    return (x if _ROUND is None else _ROUND(x)) @ w.T
+
 
 def group_norm(x, w, eps, groups=1):
     T, n = x.shape[0], x.shape[-1]
@@ -87,26 +115,26 @@ def linear_recurrence(q, k, v, decay):
 def gla_mixer(h, p, heads, dim, vdim, tau, eps):
     """p: q, k, v, g, o, norm, a1, a2, a2.b."""
     T = h.shape[0]
-    q = (h @ p["q"].T).reshape(T, heads, dim) * dim ** -0.5
-    k = (h @ p["k"].T).reshape(T, heads, dim)
-    v = (h @ p["v"].T).reshape(T, heads, vdim)
-    z = (h @ p["a1"].T) @ p["a2"].T + p["a2.b"]
+    q = lin(h, p["q"]).reshape(T, heads, dim) * dim ** -0.5
+    k = lin(h, p["k"]).reshape(T, heads, dim)
+    v = lin(h, p["v"]).reshape(T, heads, vdim)
+    z = lin(h, p["a1"]) @ p["a2"].T + p["a2.b"]  # the second factor takes unrounded rows
     f = torch.sigmoid(z).pow(1.0 / tau).reshape(T, heads, dim)
     o, _ = linear_recurrence(q, k, v, f)
     o = group_norm(o.reshape(T * heads, vdim), p["norm"], eps).reshape(T, heads * vdim)
-    return (o * silu(h @ p["g"].T)) @ p["o"].T
+    return lin(o * silu(lin(h, p["g"])), p["o"])
 
 
 def retention_mixer(h, p, heads, dim, vdim, decay, rot_dims, rot_base, eps, start=0):
     """p: q, k, v, g, o."""
     T = h.shape[0]
-    q = rotate_halves((h @ p["q"].T).reshape(T, heads, dim), rot_dims, rot_base, start)
-    k = rotate_halves((h @ p["k"].T).reshape(T, heads, dim), rot_dims, rot_base, start) * dim ** -0.5
-    v = (h @ p["v"].T).reshape(T, heads, vdim)
+    q = rotate_halves(lin(h, p["q"]).reshape(T, heads, dim), rot_dims, rot_base, start)
+    k = rotate_halves(lin(h, p["k"]).reshape(T, heads, dim), rot_dims, rot_base, start) * dim ** -0.5
+    v = lin(h, p["v"]).reshape(T, heads, vdim)
     lam = torch.as_tensor(decay, dtype=h.dtype)[None, :, None].expand(T, heads, dim)
     o, _ = linear_recurrence(q, k, v, lam)
     o = group_norm(o.reshape(T * heads, vdim), None, eps).reshape(T, heads * vdim)
-    return (o * silu(h @ p["g"].T)) @ p["o"].T
+    return lin(o * silu(lin(h, p["g"])), p["o"])
 
 
 def sigmoid_attention(q, k, v, scale, temp, bias):
@@ -117,27 +145,27 @@ def sigmoid_attention(q, k, v, scale, temp, bias):
     seen = torch.arange(T)[None, :] <= torch.arange(T)[:, None]
     for h in range(H):
         g = h // (H // G)
-        s = (q[:, h] @ k[:, g].T) * scale * temp[h] + bias[h]
-        out[:, h] = (torch.sigmoid(s) * seen) @ v[:, g]
+        s = lin(q[:, h], k[:, g]) * scale * temp[h] + bias[h]
+        out[:, h] = lin(torch.sigmoid(s) * seen, v[:, g].T)
     return out
 
 
 def attention_mixer(h, p, heads, kv_heads, dim, scale, rot_dims, rot_base, eps, start=0):
     """p: q, k, q.norm, k.norm, temp, pb, o."""
     T = h.shape[0]
-    q = (h @ p["q"].T).reshape(T, heads, dim)
-    k = (h @ p["k"].T).reshape(T, kv_heads, dim)
+    q = lin(h, p["q"]).reshape(T, heads, dim)
+    k = lin(h, p["k"]).reshape(T, kv_heads, dim)
     v = k
     q = group_norm(q.reshape(T * heads, dim), p["q.norm"], eps).reshape(T, heads, dim)
     k = group_norm(k.reshape(T * kv_heads, dim), p["k.norm"], eps).reshape(T, kv_heads, dim)
     q, k = rotate_pairs(q, rot_dims, rot_base, start), rotate_pairs(k, rot_dims, rot_base, start)
     o = sigmoid_attention(q, k, v, scale, p["temp"], p["pb"])
-    return o.reshape(T, heads * dim) @ p["o"].T
+    return lin(o.reshape(T, heads * dim), p["o"])
 
 
 def route(h, router, correction, top, n_groups, keep, scale):
     """Returns the chosen experts [T, top] and their weights [T, top]."""
-    s = torch.sigmoid(h @ router.T)
+    s = torch.sigmoid(lin(h, router))
     c = s + correction
     T, E = c.shape
     per = E // n_groups
@@ -152,21 +180,42 @@ def route(h, router, correction, top, n_groups, keep, scale):
     return idx, w / (w.sum(-1, keepdim=True) + 1e-20) * scale
 
 
-def routed_experts(h, p, n_experts, top, n_groups, keep, scale):
+def route_margins(h, router, correction, top, n_groups, keep):
+    """Per token, how far the choice is from going another way: the smaller of (the last kept group's score minus the
+    first dropped group's) and (the last chosen expert's choice score minus the first unchosen allowed one's)."""
+    c = torch.sigmoid(lin(h, router)) + correction
+    T, E = c.shape
+    per = E // n_groups
+    out = torch.full((T,), math.inf, dtype=h.dtype)
+    gscore = c.reshape(T, n_groups, per).topk(min(2, per), dim=-1).values.sum(-1)
+    order = gscore.sort(dim=-1, descending=True)
+    if keep < n_groups:
+        out = torch.minimum(out, order.values[:, keep - 1] - order.values[:, keep])
+    allowed = torch.zeros(T, n_groups, dtype=torch.bool)
+    allowed.scatter_(1, order.indices[:, :keep], True)
+    c = c.masked_fill(~allowed.repeat_interleave(per, dim=1), -math.inf).sort(dim=-1, descending=True).values
+    if top < keep * per:
+        out = torch.minimum(out, c[:, top - 1] - c[:, top])
+    return out
+
+
+def routed_experts(h, p, n_experts, top, n_groups, keep, scale, margins=None):
     """p: router, correction, e<j>.up, e<j>.down."""
     idx, w = route(h, p["router"], p["correction"], top, n_groups, keep, scale)
+    if margins is not None:
+        margins.append(route_margins(h, p["router"], p["correction"], top, n_groups, keep))
     out = torch.zeros(h.shape[0], p["e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for j in range(top):
             e = int(idx[t, j])
-            out[t] += w[t, j] * (gelu_erf(h[t] @ p[f"e{e}.up"].T) @ p[f"e{e}.down"].T)
+            out[t] += w[t, j] * lin(gelu_erf(lin(h[t], p[f"e{e}.up"])), p[f"e{e}.down"])
     return out
 
 
 def side_input(x, tokens, table, layer, dim, p, eps):
     """p: gate, proj, norm.  ``table`` holds every layer's ``dim`` values of a token side by side."""
     e = table[torch.as_tensor(tokens)][:, layer * dim:(layer + 1) * dim]
-    y = (gelu_tanh(x @ p["gate"].T) * e) @ p["proj"].T
+    y = lin(gelu_tanh(lin(x, p["gate"])) * e, p["proj"])
     return x + group_norm(y, p["norm"], eps)
 
 
@@ -187,9 +236,9 @@ def run_mixer(layer, h, p, eps, start=0):
     raise ValueError(layer["type"])
 
 
-def forward(config, weights, tokens, layers_out=None):
+def forward(config, weights, tokens, layers_out=None, margins=None):
     """Logits [T, vocab] of one sequence; ``weights`` {name: float64 tensor}.  ``layers_out`` (a list) receives the
-    stream after every layer."""
+    stream after every layer, ``margins`` (a list) every router's per-token margins."""
     eps, groups, a = config["norm"]["eps"], config["norm"]["groups"], config["postln_alpha"]
     x = weights["embed"][torch.as_tensor(tokens)]
     for i, layer in enumerate(config["layers"]):
@@ -199,10 +248,10 @@ def forward(config, weights, tokens, layers_out=None):
         if ff is not None:
             r = ff["router"]
             y = routed_experts(x, sub(weights, pre + "mlp."), r["experts"], r["top"], r["groups"]["count"],
-                               r["groups"]["keep"], r["scale"])
+                               r["groups"]["keep"], r["scale"], margins)
             x = group_norm(a * x + y, weights[pre + "norm2"], eps, groups)
         if config.get("token_side") is not None:
             x = side_input(x, tokens, weights["side.embed"], i, config["token_side"]["dim"], sub(weights, pre + "side."), eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    return group_norm(x, weights["final.norm"], eps, groups) @ weights["head"].T
+    return lin(group_norm(x, weights["final.norm"], eps, groups), weights["head"])

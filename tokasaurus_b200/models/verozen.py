@@ -70,7 +70,7 @@ def build_verozen(cfg: VerozenConfig) -> DecoderModel:
             side = TokenSideInput(W, cfg.side_dim, cfg.vocab, "side.embed", n_layers * cfg.side_dim, i * cfg.side_dim,
                                   f"{p}.side.gate", f"{p}.side.proj", f"{p}.side.norm", eps)
         blocks.append(PostNormBlock(mixer, GroupRMSNorm(W, eps, f"{p}.norm1", groups), ffn,
-                                    GroupRMSNorm(W, eps, f"{p}.norm2", groups) if ffn is not None else None,
+                                    GroupRMSNorm(W, eps, f"{p}.norm2", groups, optional=ffn is None),
                                     alpha=cfg.alpha, side=side))
     return DecoderModel(embedding=TokenEmbedding(cfg.vocab, W, "embed"), blocks=blocks,
                         head=OutputHead(cfg.vocab, W, GroupRMSNorm(W, eps, "final.norm", groups), "head"))

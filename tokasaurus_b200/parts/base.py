@@ -38,6 +38,8 @@ class WeightSpec:
     role: str = "matrix"
     # A tensor stored as float32 in the file stays float32 whatever the engine's dtype.
     keep_32bit: bool = False
+    # A tensor that a checkpoint may lack: the part then finds no entry under its name and does without.
+    optional: bool = False
 
 
 @dataclass(frozen=True)

@@ -164,11 +164,13 @@ class PostNormBlock(Part):
     weight vector); ``side`` is a part that adds a per-token input to the stream after the feed-forward
     (``parts.side_input.TokenSideInput``).  The stream stays float32: the kernel that norms a sum writes the new stream
     in both types, a sublayer's output arrives as float32 rows, as the float32 slices of a K-split product (few rows),
-    or in the activation type.  A block without a feed-forward has no second sum and no second norm."""
+    or in the activation type.  A block without a feed-forward has no second sum and no second norm; if it is given a
+    second norm all the same (an optional one, whose weight a checkpoint may or may not hold) and the weight is there,
+    the second step runs with nothing added: ``x <- norm2(alpha * x)``."""
 
     def __init__(self, mixer: Mixer, mixer_norm, ffn: FeedForward | None, ffn_norm, alpha: float = 1.0, side=None):
-        if (ffn is None) != (ffn_norm is None):
-            raise ValueError("a block has a feed-forward and its norm, or neither")
+        if ffn is not None and ffn_norm is None:
+            raise ValueError("a feed-forward needs its norm")
         self.mixer, self.mixer_norm, self.ffn, self.ffn_norm, self.side = mixer, mixer_norm, ffn, ffn_norm, side
         self.alpha = float(alpha)
         self.dtype: torch.dtype | None = None
@@ -205,6 +207,8 @@ class PostNormBlock(Part):
         stream.h = self.mixer_norm.apply_sum(stream.x, y, self.alpha)
         if self.ffn is not None:
             stream.h = self.ffn_norm.apply_sum(stream.x, self.ffn.forward(ctx, self._input(stream)), self.alpha)
+        elif self.ffn_norm is not None and self.ffn_norm.weight is not None:
+            stream.h = self.ffn_norm.apply_sum(stream.x, None, self.alpha)
         if self.side is not None:
             self.side.forward(ctx, stream, self._input(stream), out_rows)
         return stream

@@ -41,7 +41,10 @@ class GroupRMSNorm(Norm):
     the whole row is multiplied by one weight vector.  ``groups`` = 1 is the plain RMS norm.  Blocks that norm AFTER the
     residual sum (``parts.block.PostNormBlock``) hand their sum to the same kernel; ``forward`` serves an output head."""
 
-    def __init__(self, width: int, eps: float, weight_name: str, groups: int = 1):
+    def __init__(self, width: int, eps: float, weight_name: str, groups: int = 1, optional: bool = False):
+        """``optional``: checkpoints may lack the weight; ``weight`` is then None after ``bind`` and the norm's owner
+        leaves the norm out."""
+        self.optional = bool(optional)
         if groups <= 0 or width % groups:
             raise ValueError(f"a row of {width} values does not divide into {groups} equal parts")
         self.width, self.eps, self.weight_name, self.groups = width, float(eps), weight_name, int(groups)
@@ -49,13 +52,13 @@ class GroupRMSNorm(Norm):
         self.out_dtype: torch.dtype | None = None
 
     def weight_specs(self):
-        return (WeightSpec(self.weight_name, (self.width,), role="vector"),)
+        return (WeightSpec(self.weight_name, (self.width,), role="vector", optional=self.optional),)
 
     def kernel_modules(self, dtype):
         return (("post_norm.cu", None),)
 
     def bind(self, weights, rt) -> None:
-        self.weight = weights[self.weight_name]
+        self.weight = weights.get(self.weight_name) if self.optional else weights[self.weight_name]
         self.out_dtype = rt.dtype
 
     def apply_sum(self, x: torch.Tensor, y, alpha: float) -> torch.Tensor | None:

@@ -84,7 +84,7 @@ def load_weights(folder: str | Path, specs: Iterable[WeightSpec], engine_dtype: 
     specs = list(specs)
     where = _files_by_name(folder)
     wanted = {s.name: s for s in specs}
-    missing = [n for n in wanted if n not in where]
+    missing = [n for n in wanted if n not in where and not wanted[n].optional]
     extra = sorted(n for n in where if n not in wanted)
     unexpected = [n for n in extra if not any(fnmatch.fnmatch(n, p) for p in ignore)]
     passed_over = [n for n in extra if n not in unexpected]

@@ -35,6 +35,8 @@ def random_tensors(specs: Iterable[WeightSpec], seed: int, std: float = 0.02, no
     g.manual_seed(int(seed))
     out: dict[str, torch.Tensor] = {}
     for s in specs:
+        if s.optional:  # a tensor that checkpoints may lack: random models lack it
+            continue
         if any(d < 0 for d in s.shape):  # a size that only a weight file knows: random weights take 16
             s = WeightSpec(s.name, tuple(16 if d < 0 else d for d in s.shape), s.role, s.keep_32bit)
         if s.role == "table":
