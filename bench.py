@@ -2,7 +2,7 @@
 random weights (the metric and configuration of BASELINE.json's configs[2]).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3|4]
-    python bench.py --design sozurax|daborax   (another workload, see run_design; the default workload and its output line are unchanged)
+    python bench.py --design sozurax|daborax|verozen   (another workload, see run_design; the default workload and its output line are unchanged)
 
 Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8, each request holding a
 2,048-token prompt in the cache, timed on the device with CUDA events around K decode steps
@@ -160,7 +160,7 @@ def prefill_flops(m: dict, T: int, rows: int = 1) -> float:
     return linear + attention
 
 
-TIMED_OPS = ("scaled_norm_add", "cast_rows", "add_sinusoid", "clamped_glu", "gated_group_norm", "ssm_prep", "decay_walk",
+TIMED_OPS = ("sum_group_norm", "gelu_gate_rows", "gla_gates", "rotate_scale", "linear_out_f32", "scaled_norm_add", "cast_rows", "add_sinusoid", "clamped_glu", "gated_group_norm", "ssm_prep", "decay_walk",
              "sink_attn_prep", "attn_sink", "attn_sink_tc", "silu_cols", "gemm_tcgen05_clamped", "add_layernorm", "add_layernorm_conv1", "short_conv", "polynorm", "gated_recurrence", "latent_prep",
              "rotate_pairs", "latent_attn", "moe_route", "moe_order", "moe_gather", "moe_gemm", "moe_combine",
              "gemm_tcgen05_grouped", "embed_gather", "add_rmsnorm", "rope_kv_write", "rope_kv_write_partials", "linear_decode", "linear_smallm",
@@ -679,6 +679,29 @@ def daborax_configs(name: str) -> dict:
     return dict(daborax=dab, llama=llama)
 
 
+def verozen_configs(name: str) -> dict:
+    """Layer sizes for ``--design verozen``: two sizes that resemble a real model's layers, each as a Verozen decoder
+    (retention, gated linear attention, sigmoid attention whose values are the keys, gated linear attention again;
+    every layer under norms after the residual sums, with routed GELU experts whose chosen inner sizes add up to the
+    dense arm's, and a per-token side input) and as the closest existing model, the Daborax decoder of
+    ``daborax_configs`` (the same walk kernel under its linear attention and state space, the same attention kernel
+    file, norms around float32 sublayer outputs) at the same width, depth, vocabulary and head sizes."""
+    sizes = dict(w2048=dict(width=2048, heads=16, att_heads=16, att_kv=4, experts=16, top=4, expert_ff=2048, groups=4, keep=2),
+                 w4096=dict(width=4096, heads=32, att_heads=32, att_kv=8, experts=16, top=4, expert_ff=3584, groups=4, keep=2))
+    z = sizes[name]
+    H = z["heads"]
+    mlp = dict(kind="moe", expert=dict(ff=z["expert_ff"]),
+               router=dict(experts=z["experts"], top=z["top"], scale=2.5, groups=dict(count=z["groups"], keep=z["keep"])))
+    ret = dict(type="retention", mixer=dict(heads=H, dim=128, vdim=128, rot=dict(dims=128, base=10000.0),
+                                            decay=[1.0 - 2.0 ** -(5 + 6 * h / (H - 1)) for h in range(H)]), mlp=mlp)
+    gla = dict(type="gla", mixer=dict(heads=H, dim=128, vdim=128, tau=16.0, rank=64), mlp=mlp)
+    att = dict(type="attention", mixer=dict(heads=z["att_heads"], kv_heads=z["att_kv"], dim=128, vdim=128, scale=128 ** -0.5,
+                                            rot=dict(dims=64, base=1000000.0)), mlp=mlp)
+    ver = dict(architecture="Verozen", vocab=32000, width=z["width"], norm=dict(eps=1e-6, groups=4), postln_alpha=2.0,
+               token_side=dict(dim=256), layers=[ret, gla, att, gla])
+    return dict(verozen=ver, daborax=daborax_configs(name)["daborax"])
+
+
 def design_configs(name: str) -> dict:
     """Layer sizes for ``--design sozurax``: two sizes that resemble a real model's layers, each as a Sozurax decoder
     (a recurrent layer with a dense feed-forward, a latent-attention layer with routed experts, a second recurrent
@@ -708,8 +731,8 @@ def design_configs(name: str) -> dict:
 
 
 def run_design(args) -> dict:
-    """``--design sozurax|daborax``: prefill (one 2,048-token prompt in one step) and decode (batch 8 and 64, prompts of
-    2,048 tokens in the cache) of that decoder at two layer sizes beside a Llama decoder of equal size, random weights,
+    """``--design sozurax|daborax|verozen``: prefill (one 2,048-token prompt in one step) and decode (batch 8 and 64, prompts of
+    2,048 tokens in the cache) of that decoder at two layer sizes beside the closest existing decoder of equal size, random weights,
     bfloat16, with the CUDA-event time of each kind of kernel in one prefill step and one decode step of both."""
     import numpy as np
     import torch
@@ -722,7 +745,7 @@ def run_design(args) -> dict:
     peaks, peak_src = load_peaks()
     prompt_len, page_size = 2048, 16
     out = dict(design=args.design, dtype="bf16", data="synthetic", peaks=dict(peaks, source=peak_src), sizes={})
-    configs_of = daborax_configs if args.design == "daborax" else design_configs
+    configs_of = dict(daborax=daborax_configs, sozurax=design_configs, verozen=verozen_configs)[args.design]
     for size in ("w2048", "w4096"):
         res = {}
         for arch, cfg in configs_of(size).items():
@@ -833,9 +856,9 @@ def main() -> int:
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
                     help="2: the headline metric (default); 3 and 4: the further workloads, see run_further")
     ap.add_argument("--design-arch", default=None, help="with --design: only this arm (the design's name or 'llama')")
-    ap.add_argument("--design", default=None, choices=["sozurax", "daborax"],
+    ap.add_argument("--design", default=None, choices=["sozurax", "daborax", "verozen"],
                     help="instead of the headline workload: this design's prefill and decode at two layer sizes beside "
-                         "the Llama decoder of equal size (see run_design)")
+                         "the closest existing decoder of equal size (see run_design)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

@@ -118,7 +118,8 @@ class ExpertsConfig:
         groups = _pos_int(g, "count", where + ".router.groups") if "count" in g else 1
         keep = _pos_int(g, "keep", where + ".router.groups") if "keep" in g else groups
         if experts % groups or keep > groups or top > keep * (experts // groups):
-            raise ConfigError(f"{where}.router: {experts} experts in {groups} groups of which {keep} are kept cannot give {top}")
+            raise ConfigError(f"{where}.router: experts={experts} in groups.count={groups} of which groups.keep={keep} "
+                              f"are kept cannot give top={top}")
         return ExpertsConfig(_pos_int(d.get("expert") or {}, "ff", where + ".expert"), experts, top, groups, keep,
                              _number(r, "scale", where + ".router", 1.0))
 

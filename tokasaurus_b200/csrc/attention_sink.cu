@@ -495,8 +495,8 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
 
 constexpr size_t TC_SMEM = (size_t)2 * KT * RS * sizeof(bf16);
 
-// Portions: block b takes the b-th 64-query tile of the step's requests that bring more than one token; blockIdx.y is
-// the query head.
+// Portions: blockIdx.y counts the 64-query tiles of the step's requests that bring more than one token from the end;
+// blockIdx.x is the query head.
 __global__ void __launch_bounds__(128)
 attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
@@ -507,7 +507,9 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* bufs = reinterpret_cast<bf16*>(smem_raw);
   trigger_dependents();
-  int s = 0, tile = blockIdx.x;
+  // the last tiles first, for all heads: without a window a portion's last queries see the most keys, and the blocks
+  // that start first should be the ones that run longest (blocks start in the order of blockIdx.x, then blockIdx.y)
+  int s = 0, tile = (int)gridDim.y - 1 - (int)blockIdx.y;
   for (; s < n_seqs; s++) {
     const int n = seq_q_len[s];
     const int tiles = n > 1 ? (n + KT - 1) / KT : 0;
@@ -517,7 +519,7 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
   if (s >= n_seqs) return;
   grid_dependency_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  const int h = blockIdx.y, kvh = h / (nh / nkv);
+  const int h = blockIdx.x, kvh = h / (nh / nkv);
   const int n_q = seq_q_len[s], start = seq_q_start[s];
   const int pos0 = seq_kv_len[s] - n_q;  // position of the portion's first token
   const int r0 = tile * KT;              // first query of the tile within the portion
@@ -780,7 +782,8 @@ TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache
   }
   if (rc != 0 || !portions) return rc;
   const int tiles = n_tokens / KT + n_seqs;  // no step of this shape has more 64-query tiles
-  return launch_pdl(attn_sink_tiles_kernel, dim3(tiles, nh), dim3(128), TC_SMEM, (cudaStream_t)st, (const bf16*)q,
+  if (tiles > 65535) return -3;
+  return launch_pdl(attn_sink_tiles_kernel, dim3(nh, tiles), dim3(128), TC_SMEM, (cudaStream_t)st, (const bf16*)q,
                     (bf16*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, n_seqs,
                     sinks, nh, nkv, page_size, scale, softcap, window, num_pages, status, head_scale, head_bias);
 }

@@ -418,39 +418,56 @@ namespace {
 // exp(log_sigmoid(z) / tau) with log_sigmoid(z) = min(z, 0) - log1p(exp(-|z|)); and q (q_cols columns at q_off of
 // the same rows) times q_scale, in place.
 constexpr int GT = 8;
+// A block owns GT tokens and blockDim.x columns (grid: token groups x column tiles), a thread one column of all GT
+// tokens: the second factor's values come sixteen rows at a time (sixteen loads in flight a thread; a thread that
+// walked all of a row's columns one load after the other took the same 0.2 ms for 8 tokens as for 2,048), the tokens'
+// low-rank rows lie in shared memory rank-major, so that two 16-byte reads bring one rank's values of all GT tokens to
+// the whole warp (one 4-byte read a token and rank made shared memory the bound at thousands of tokens).  The sum over
+// the rank runs in order, whatever the tiling.
+static_assert(GT == 8, "two float4 a rank");
 __global__ void __launch_bounds__(256)
 gla_gates_kernel(float* __restrict__ proj, int stride, int low_off, int rank, const float* __restrict__ a2t,
                  const float* __restrict__ bias, float inv_tau, int C, float* __restrict__ f, int q_off, int q_cols,
                  float q_scale, int n_tokens) {
-  extern __shared__ float low[];  // [GT][rank]
+  extern __shared__ __align__(16) float low[];  // [rank][GT], tokens past the step's last zero
   trigger_dependents();
   grid_dependency_wait();
   const int t0 = blockIdx.x * GT;
   const int nt = min(GT, n_tokens - t0);
-  for (int idx = threadIdx.x; idx < nt * rank; idx += blockDim.x) {
+  for (int idx = threadIdx.x; idx < GT * rank; idx += blockDim.x) {
     const int t = idx / rank, r = idx - t * rank;
-    low[idx] = proj[(size_t)(t0 + t) * stride + low_off + r];
+    low[r * GT + t] = t < nt ? proj[(size_t)(t0 + t) * stride + low_off + r] : 0.f;
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c < C) {
     float z[GT];
     const float b = bias ? bias[c] : 0.f;
 #pragma unroll
     for (int t = 0; t < GT; t++) z[t] = b;
-    for (int r = 0; r < rank; r++) {
-      const float w = a2t[(size_t)r * C + c];
+    auto add = [&](float w, int r) {
+      const float4 lo = *reinterpret_cast<const float4*>(low + r * GT);
+      const float4 hi = *reinterpret_cast<const float4*>(low + r * GT + 4);
+      z[0] = fmaf(w, lo.x, z[0]); z[1] = fmaf(w, lo.y, z[1]); z[2] = fmaf(w, lo.z, z[2]); z[3] = fmaf(w, lo.w, z[3]);
+      z[4] = fmaf(w, hi.x, z[4]); z[5] = fmaf(w, hi.y, z[5]); z[6] = fmaf(w, hi.z, z[6]); z[7] = fmaf(w, hi.w, z[7]);
+    };
+    int r = 0;
+    for (; r + 16 <= rank; r += 16) {
+      float w[16];
 #pragma unroll
-      for (int t = 0; t < GT; t++)
-        if (t < nt) z[t] = fmaf(w, low[t * rank + r], z[t]);
+      for (int i = 0; i < 16; i++) w[i] = a2t[(size_t)(r + i) * C + c];
+#pragma unroll
+      for (int i = 0; i < 16; i++) add(w[i], r + i);
     }
+    for (; r < rank; r++) add(a2t[(size_t)r * C + c], r);
 #pragma unroll
     for (int t = 0; t < GT; t++)
       if (t < nt) f[(size_t)(t0 + t) * C + c] = expf((fminf(z[t], 0.f) - log1pf(expf(-fabsf(z[t])))) * inv_tau);
   }
   if (q_scale != 1.f)
-    for (int idx = threadIdx.x; idx < nt * q_cols; idx += blockDim.x) {
-      const int t = idx / q_cols, c = idx - t * q_cols;
-      proj[(size_t)(t0 + t) * stride + q_off + c] *= q_scale;
+    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < nt * q_cols; idx += gridDim.y * blockDim.x) {
+      const int t = idx / q_cols, cc = idx - t * q_cols;
+      proj[(size_t)(t0 + t) * stride + q_off + cc] *= q_scale;
     }
 }
 
@@ -503,7 +520,8 @@ TKB_EXPORT int tkb_gla_gates(float* proj, int stride, int low_off, int rank, con
                              void* st) {
   if (n_tokens <= 0) return 0;
   if (rank <= 0 || C <= 0 || (size_t)GT * rank * sizeof(float) > 48 * 1024) return -2;
-  return launch_pdl(gla_gates_kernel, dim3((n_tokens + GT - 1) / GT), dim3(256), (size_t)GT * rank * sizeof(float),
+  if ((C + 255) / 256 > 65535) return -2;
+  return launch_pdl(gla_gates_kernel, dim3((n_tokens + GT - 1) / GT, (C + 255) / 256), dim3(256), (size_t)GT * rank * sizeof(float),
                     (cudaStream_t)st, proj, stride, low_off, rank, a2t, bias, inv_tau, C, f, q_off, q_cols, q_scale,
                     n_tokens);
 }
