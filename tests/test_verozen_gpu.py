@@ -112,12 +112,13 @@ def test_head_norm_with_shared_weight_and_silu_gate(ops, dtype, heads, vdim):
         assert rel_err(out.float().cpu(), want) < TOL[dtype]
 
 
-@pytest.mark.parametrize("C,rank,tau", [(48, 5, 8.0), (192, 16, 16.0), (72, 40, 1.0), (8, 1, 3.0)])
-def test_decays_of_gated_linear_attention(ops, C, rank, tau):
+@pytest.mark.parametrize("T", [21, 531])  # no multiples of the tokens a block takes
+@pytest.mark.parametrize("C,rank,tau", [(48, 5, 8.0), (192, 16, 16.0), (72, 40, 1.0), (8, 1, 3.0), (300, 19, 4.0)])
+def test_decays_of_gated_linear_attention(ops, C, rank, tau, T):
     """f = sigmoid(low A2^T + b)^(1 / tau) from the low-rank columns of the projections, also where the sigmoid is
-    within rounding of 0 or 1; q scaled in place; the other columns untouched."""
+    within rounding of 0 or 1; q scaled in place; the other columns untouched.  A token's decays do not depend on how
+    many tokens the step brings."""
     g = torch.Generator().manual_seed(C)
-    T = 21  # no multiple of the tokens a block takes
     proj = torch.randn(T, C + 7 + rank, generator=g)
     proj[0, C + 7:] *= 40
     proj[1, C + 7:] *= -40
@@ -134,6 +135,11 @@ def test_decays_of_gated_linear_attention(ops, C, rank, tau):
     assert bool(((f.cpu().double() - want).abs() <= 1e-6 + 2.5e-7 * spread * slope).all())
     assert rel_err(pd[:, :C].cpu(), proj[:, :C].double() * 0.37) < 1e-6
     assert float((pd[:, C:] - proj[:, C:].to(DEV)).abs().max()) == 0.0
+    if T > 500:
+        few = torch.empty(40, C, device=DEV)
+        part = proj[T - 40:].to(DEV).contiguous()
+        ops.gla_gates(part, C + 7, rank, a2.t().contiguous().to(DEV), b.to(DEV), tau, few, 0, C, 0.37, walk_defines(ops, 16, 16))
+        assert torch.equal(few, f[T - 40:])
 
 
 @pytest.mark.parametrize("heads,dim,rot,pairs", [(3, 16, 16, False), (2, 24, 8, False), (4, 32, 16, True), (1, 10, 10, True), (2, 12, 0, False)])

@@ -81,6 +81,7 @@ MODELS = {
 }
 
 MIN_MARGIN = 2e-4  # of a sigmoid score: hundreds of times what float32 sums of a router's width can move one
+TIER_MARGIN = 0.2  # between tiers: far more than bfloat16 rounding of a router's input moves a score
 
 
 def adjust(name: str, t: torch.Tensor, g: torch.Generator, tiered: bool) -> torch.Tensor:
@@ -135,7 +136,7 @@ def make_models(root, names=None):
                 want[rid] = plain.forward(spec["config"], w64, t, margins=ms).numpy()
                 noise[rid] = rounding_noise(spec["config"], w64, t, want[rid], variant_dtype(kind))
                 margin = min([margin] + [float(m.min()) for m in ms])
-            assert margin > (MIN_MARGIN if kind == "dyn" else 0.2), \
+            assert margin > (MIN_MARGIN if kind == "dyn" else TIER_MARGIN), \
                 f"model {name} ({kind}): a router's choice rests on a margin of {margin:.2g}"
             out[(name, kind)] = dict(folder=folder, config=spec["config"], weights=w64, reqs=reqs, want=want,
                                      noise=noise, page=spec["page"], margin=margin)

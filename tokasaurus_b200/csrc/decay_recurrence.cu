@@ -417,18 +417,19 @@ namespace {
 // [rank, C], the transposed second factor; low = A1 h, rank columns of the projections), f = sigmoid(z)^(1/tau) =
 // exp(log_sigmoid(z) / tau) with log_sigmoid(z) = min(z, 0) - log1p(exp(-|z|)); and q (q_cols columns at q_off of
 // the same rows) times q_scale, in place.
-constexpr int GT = 8;
 // A block owns GT tokens and blockDim.x columns (grid: token groups x column tiles), a thread one column of all GT
 // tokens: the second factor's values come sixteen rows at a time (sixteen loads in flight a thread; a thread that
 // walked all of a row's columns one load after the other took the same 0.2 ms for 8 tokens as for 2,048), the tokens'
-// low-rank rows lie in shared memory rank-major, so that two 16-byte reads bring one rank's values of all GT tokens to
-// the whole warp (one 4-byte read a token and rank made shared memory the bound at thousands of tokens).  The sum over
-// the rank runs in order, whatever the tiling.
-static_assert(GT == 8, "two float4 a rank");
+// low-rank rows lie in shared memory rank-major, so that GT / 4 16-byte reads bring one rank's values of all GT tokens
+// to the whole warp (one 4-byte read a token and rank made shared memory the bound at thousands of tokens).  The sum
+// over the rank runs in order, whatever the tiling.  GT = 8 at every step size: with 32 tokens a block (a quarter of
+// the second factor's traffic out of the L2) 2,048 tokens took 73 us against 49 us.
+template <int GT>
 __global__ void __launch_bounds__(256)
 gla_gates_kernel(float* __restrict__ proj, int stride, int low_off, int rank, const float* __restrict__ a2t,
                  const float* __restrict__ bias, float inv_tau, int C, float* __restrict__ f, int q_off, int q_cols,
                  float q_scale, int n_tokens) {
+  static_assert(GT % 4 == 0, "whole float4 a rank");
   extern __shared__ __align__(16) float low[];  // [rank][GT], tokens past the step's last zero
   trigger_dependents();
   grid_dependency_wait();
@@ -446,10 +447,14 @@ gla_gates_kernel(float* __restrict__ proj, int stride, int low_off, int rank, co
 #pragma unroll
     for (int t = 0; t < GT; t++) z[t] = b;
     auto add = [&](float w, int r) {
-      const float4 lo = *reinterpret_cast<const float4*>(low + r * GT);
-      const float4 hi = *reinterpret_cast<const float4*>(low + r * GT + 4);
-      z[0] = fmaf(w, lo.x, z[0]); z[1] = fmaf(w, lo.y, z[1]); z[2] = fmaf(w, lo.z, z[2]); z[3] = fmaf(w, lo.w, z[3]);
-      z[4] = fmaf(w, hi.x, z[4]); z[5] = fmaf(w, hi.y, z[5]); z[6] = fmaf(w, hi.z, z[6]); z[7] = fmaf(w, hi.w, z[7]);
+#pragma unroll
+      for (int j = 0; j < GT / 4; j++) {
+        const float4 l4 = *reinterpret_cast<const float4*>(low + r * GT + 4 * j);
+        z[4 * j] = fmaf(w, l4.x, z[4 * j]);
+        z[4 * j + 1] = fmaf(w, l4.y, z[4 * j + 1]);
+        z[4 * j + 2] = fmaf(w, l4.z, z[4 * j + 2]);
+        z[4 * j + 3] = fmaf(w, l4.w, z[4 * j + 3]);
+      }
     };
     int r = 0;
     for (; r + 16 <= rank; r += 16) {
@@ -464,11 +469,28 @@ gla_gates_kernel(float* __restrict__ proj, int stride, int low_off, int rank, co
     for (int t = 0; t < GT; t++)
       if (t < nt) f[(size_t)(t0 + t) * C + c] = expf((fminf(z[t], 0.f) - log1pf(expf(-fabsf(z[t])))) * inv_tau);
   }
-  if (q_scale != 1.f)
-    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < nt * q_cols; idx += gridDim.y * blockDim.x) {
-      const int t = idx / q_cols, cc = idx - t * q_cols;
-      proj[(size_t)(t0 + t) * stride + q_off + cc] *= q_scale;
+  if (q_scale != 1.f) {
+    // eight loads in flight a thread, then the eight stores (one value at a time, every round trip to memory waited for
+    // the one before: 8 tokens took as long as the decays themselves)
+    const int total = nt * q_cols, step = gridDim.y * blockDim.x;
+    int idx = blockIdx.y * blockDim.x + threadIdx.x;
+    for (; idx + 7 * step < total; idx += 8 * step) {
+      float* at[8];
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int j = idx + i * step, t = j / q_cols;
+        at[i] = proj + (size_t)(t0 + t) * stride + q_off + (j - t * q_cols);
+        v[i] = *at[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; i++) *at[i] = v[i] * q_scale;
     }
+    for (; idx < total; idx += step) {
+      const int t = idx / q_cols;
+      proj[(size_t)(t0 + t) * stride + q_off + (idx - t * q_cols)] *= q_scale;
+    }
+  }
 }
 
 // Rotation by position of the q and k heads of float32 rows, in place: the first rot_dims channels of a head, channel i
@@ -519,11 +541,11 @@ TKB_EXPORT int tkb_gla_gates(float* proj, int stride, int low_off, int rank, con
                              float inv_tau, int C, float* f, int q_off, int q_cols, float q_scale, int n_tokens,
                              void* st) {
   if (n_tokens <= 0) return 0;
-  if (rank <= 0 || C <= 0 || (size_t)GT * rank * sizeof(float) > 48 * 1024) return -2;
+  if (rank <= 0 || C <= 0 || (size_t)8 * rank * sizeof(float) > 48 * 1024) return -2;
   if ((C + 255) / 256 > 65535) return -2;
-  return launch_pdl(gla_gates_kernel, dim3((n_tokens + GT - 1) / GT, (C + 255) / 256), dim3(256), (size_t)GT * rank * sizeof(float),
-                    (cudaStream_t)st, proj, stride, low_off, rank, a2t, bias, inv_tau, C, f, q_off, q_cols, q_scale,
-                    n_tokens);
+  return launch_pdl(gla_gates_kernel<8>, dim3((n_tokens + 7) / 8, (C + 255) / 256), dim3(256),
+                    (size_t)8 * rank * sizeof(float), (cudaStream_t)st, proj, stride, low_off, rank, a2t, bias, inv_tau, C,
+                    f, q_off, q_cols, q_scale, n_tokens);
 }
 
 TKB_EXPORT int tkb_rotate_scale(float* proj, int stride, int q_off, int k_off, int heads, int dim, int rot_dims,

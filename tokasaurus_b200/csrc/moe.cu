@@ -38,16 +38,31 @@ moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ wr, const f
   const float* w3 = wr + (size_t)min(e0 + 3, E - 1) * H;
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
   if ((H & 3) == 0 && (((uintptr_t)wr) & 15) == 0) {
-    // sixteen bytes of every weight row a lane and pass
-#pragma unroll 2
-    for (int i = lane * 4; i < H; i += 128) {
-      const float x[4] = {to_float(hr[i]), to_float(hr[i + 1]), to_float(hr[i + 2]), to_float(hr[i + 3])};
-      const float4 v0 = *reinterpret_cast<const float4*>(w0 + i), v1 = *reinterpret_cast<const float4*>(w1 + i);
-      const float4 v2 = *reinterpret_cast<const float4*>(w2 + i), v3 = *reinterpret_cast<const float4*>(w3 + i);
-      a0 = fmaf(x[0], v0.x, fmaf(x[1], v0.y, fmaf(x[2], v0.z, fmaf(x[3], v0.w, a0))));
-      a1 = fmaf(x[0], v1.x, fmaf(x[1], v1.y, fmaf(x[2], v1.z, fmaf(x[3], v1.w, a1))));
-      a2 = fmaf(x[0], v2.x, fmaf(x[1], v2.y, fmaf(x[2], v2.z, fmaf(x[3], v2.w, a2))));
-      a3 = fmaf(x[0], v3.x, fmaf(x[1], v3.y, fmaf(x[2], v3.z, fmaf(x[3], v3.w, a3))));
+    // sixteen bytes of every weight row a lane and pass; the loads of four passes are issued before their sums (with
+    // two in flight, eight tokens of width 2,048 waited eight times for memory: 18 us a layer); passes beyond the row
+    // add zeros, and the sums keep their order
+    for (int i0 = lane * 4; i0 < H; i0 += 512) {
+      float4 v[4][4];
+      float x[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int i = i0 + 128 * u;
+        const bool in = i < H;
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+        v[u][0] = in ? *reinterpret_cast<const float4*>(w0 + i) : zero;
+        v[u][1] = in ? *reinterpret_cast<const float4*>(w1 + i) : zero;
+        v[u][2] = in ? *reinterpret_cast<const float4*>(w2 + i) : zero;
+        v[u][3] = in ? *reinterpret_cast<const float4*>(w3 + i) : zero;
+#pragma unroll
+        for (int c = 0; c < 4; c++) x[u][c] = in ? to_float(hr[i + c]) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        a0 = fmaf(x[u][0], v[u][0].x, fmaf(x[u][1], v[u][0].y, fmaf(x[u][2], v[u][0].z, fmaf(x[u][3], v[u][0].w, a0))));
+        a1 = fmaf(x[u][0], v[u][1].x, fmaf(x[u][1], v[u][1].y, fmaf(x[u][2], v[u][1].z, fmaf(x[u][3], v[u][1].w, a1))));
+        a2 = fmaf(x[u][0], v[u][2].x, fmaf(x[u][1], v[u][2].y, fmaf(x[u][2], v[u][2].z, fmaf(x[u][3], v[u][2].w, a2))));
+        a3 = fmaf(x[u][0], v[u][3].x, fmaf(x[u][1], v[u][3].y, fmaf(x[u][2], v[u][3].z, fmaf(x[u][3], v[u][3].w, a3))));
+      }
     }
   } else {
 #pragma unroll 4
