@@ -59,7 +59,7 @@ class RequestCache:
     request: object
     slot: int
     tables: list[list[int]]  # per group; -1 where a page was given back behind a window
-    released: list[int] = field(default_factory=list)  # per group: leading pages already given back
+    released: list[int] = field(default_factory=list)  # per group: pages already given back (behind the kept first ones)
     arrays: dict[int, np.ndarray] = field(default_factory=dict)  # per group: tables[g] as int32, made on demand
 
     def live_pages(self, g: int) -> list[int]:
@@ -109,7 +109,8 @@ class CacheManager:
                 if g is None:
                     pool = num_pages
                     if need.window and max_step_tokens is not None:
-                        pool = min(num_pages, max_requests * (self.pages_for(need.window + max_step_tokens + 1) + 1))
+                        pool = min(num_pages, max_requests * (self.pages_for(need.window + max_step_tokens + 1) + 1
+                                                              + self.pages_for(need.keep_first)))
                     g = CacheGroup(len(self.groups), need, [], PageAllocator(pool))
                     by_need[need] = g
                     self.groups.append(g)
@@ -135,6 +136,12 @@ class CacheManager:
     # ------------------------------------------------------------------ sizes
     def pages_for(self, n_tokens: int) -> int:
         return (n_tokens + self.page_size - 1) // self.page_size
+
+    def kept_pages(self, g: int) -> int:
+        """Leading pages of a request that a windowed group never gives back: those of the first positions its mixers
+        keep in sight."""
+        need = self.groups[g].need
+        return self.pages_for(need.keep_first) if need.window and need.keep_first else 0
 
     def device_bytes(self) -> int:
         return sum(self.device_bytes_by_group())
@@ -193,7 +200,9 @@ class CacheManager:
 
     def release_behind_window(self, request: object, n_processed: int) -> int:
         """After ``n_processed`` tokens of the request have gone through the model, give back the
-        pages of windowed groups that no later token can see.  Returns how many pages came back."""
+        pages of windowed groups that no later token can see (the pages of the first ``keep_first`` positions stay:
+        every later token sees them).  ``released`` counts the pages given back, which follow the kept ones.  Returns
+        how many pages came back."""
         rc = self.requests[request]
         count = 0
         for g in self.groups:
@@ -203,14 +212,14 @@ class CacheManager:
             # the next query sits at position >= n_processed and sees keys > position - w
             first_visible = max(0, n_processed - w + 1)
             full_pages_behind = min(first_visible // self.page_size, len(rc.tables[g.index]))
-            lo = rc.released[g.index]
+            lo = min(self.kept_pages(g.index), full_pages_behind) + rc.released[g.index]
             if full_pages_behind > lo:
                 pages = rc.tables[g.index][lo:full_pages_behind]
                 g.allocator.release(pages, request)
                 for i in range(lo, full_pages_behind):
                     rc.tables[g.index][i] = -1
                 rc.arrays.pop(g.index, None)
-                rc.released[g.index] = full_pages_behind
+                rc.released[g.index] += full_pages_behind - lo
                 count += len(pages)
         return count
 

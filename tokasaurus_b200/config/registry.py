@@ -86,4 +86,4 @@ def _ensure_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from tokasaurus_b200.models import daborax, llama, sozurax, verozen  # noqa: F401  (they register themselves)
+        from tokasaurus_b200.models import bibalix, daborax, llama, sozurax, verozen  # noqa: F401  (they register themselves)

@@ -35,9 +35,20 @@
 // once a token), and cache the key as projected (before norm and rotation) as the value (values_are_keys: QK == VD, the
 // projections hold no v).
 //
-// Compile with -DTKB_QK=<query/key size> -DTKB_VD=<value size> [-DTKB_SIGMOID=1].
+// Several attention maps a head (-DTKB_MAPS=2): q holds heads * MAPS query vectors, head by head [map 0, map 1, ...], the
+// projections as many key vectors a key/value head, and a cached row is [k of map 0 | k of map 1 | ... | v].  Every map
+// is an attention of its own over the same values; the kernels treat (head, map) as a query head whose keys start
+// MAP * QK values into the row, and leave the maps' outputs side by side in float32 [rows, heads, MAPS, VD] (what
+// combines them wants them unrounded).  diff_combine (MAPS == 2) is the differential form's combination:
+// o = a_0 - lambda a_1, divided by its root mean square over VD, times a number and the sigmoid of a per-head gate.
+//
+// keep_first: with a window, the first keep_first positions of a request stay visible to every later query
+// (position i sees j if j <= i and (i - j < window or j < keep_first)).
+//
+// Compile with -DTKB_QK=<query/key size> -DTKB_VD=<value size> [-DTKB_SIGMOID=1] [-DTKB_MAPS=2].
 #include "common.cuh"
 #include <float.h>
+#include <type_traits>
 
 #if !defined(TKB_QK) || !defined(TKB_VD)
 #error "compile with -DTKB_QK=<query/key size> -DTKB_VD=<value size>"
@@ -46,6 +57,10 @@ static_assert(TKB_QK >= 1 && TKB_QK <= 512 && TKB_VD >= 1 && TKB_VD <= 512, "hea
 #ifndef TKB_SIGMOID
 #define TKB_SIGMOID 0
 #endif
+#ifndef TKB_MAPS
+#define TKB_MAPS 1
+#endif
+static_assert(TKB_MAPS >= 1 && TKB_MAPS <= 4, "one to four attention maps a head");
 
 using namespace tkb;
 
@@ -53,7 +68,9 @@ namespace {
 
 constexpr int QK = TKB_QK;
 constexpr int VD = TKB_VD;
-constexpr int ROW = QK + VD;
+constexpr int MAPS = TKB_MAPS;
+constexpr int KW = MAPS * QK;  // key values of a cached row; the value follows them
+constexpr int ROW = KW + VD;
 constexpr int WARPS = 4;
 constexpr int DPL = (VD + 31) / 32;
 constexpr bool SIGMOID = TKB_SIGMOID != 0;
@@ -123,9 +140,10 @@ sink_attn_prep_kernel(const float* __restrict__ qkv, int stride, const float* __
     }
     __syncthreads();
   }
-  // q heads and k heads: one warp a head
-  for (int hh = warp; hh < nh + nkv; hh += nwarps) {
-    const int off = hh * QK;  // k heads follow the q heads in the row
+  // q vectors and k vectors (MAPS of each a head): one warp a vector
+  const int nhq = nh * MAPS, nkk = nkv * MAPS;
+  for (int hh = warp; hh < nhq + nkk; hh += nwarps) {
+    const int off = hh * QK;  // the k vectors follow the q vectors in the row
     float ss = 0.f;
     for (int d = lane; d < QK; d += 32) {
       const float v = row[off + d] + (bias ? bias[off + d] : 0.f);
@@ -134,10 +152,11 @@ sink_attn_prep_kernel(const float* __restrict__ qkv, int stride, const float* __
     ss = warp_sum(ss);
     const float r = unit_norm ? rsqrtf(ss / (float)QK + eps) : 1.f;
     T* dst = nullptr;
-    if (hh < nh) dst = q_out + (size_t)t * nh * QK + off;
-    else if (page >= 0) dst = cache + (((size_t)page * nkv + (hh - nh)) * page_size + slot) * ROW;
+    if (hh < nhq) dst = q_out + (size_t)t * nhq * QK + off;
+    else if (page >= 0)
+      dst = cache + (((size_t)page * nkv + (hh - nhq) / MAPS) * page_size + slot) * ROW + ((hh - nhq) % MAPS) * QK;
     if (dst != nullptr) {
-      const float* w = norm_w ? norm_w + (hh < nh ? 0 : QK) : nullptr;
+      const float* w = norm_w ? norm_w + (hh < nhq ? 0 : QK) : nullptr;
       auto val = [&](int d) { return (row[off + d] + (bias ? bias[off + d] : 0.f)) * r * (w ? w[d] : 1.f); };
       for (int i = lane; i < half; i += 32) {
         const int a = rot_pairs ? 2 * i : i, b = rot_pairs ? 2 * i + 1 : i + half;
@@ -149,23 +168,27 @@ sink_attn_prep_kernel(const float* __restrict__ qkv, int stride, const float* __
     }
   }
   if (page >= 0) {
-    const int voff = values_are_keys ? nh * QK : (nh + nkv) * QK;  // the keys as projected are the values
+    const int voff = values_are_keys ? nhq * QK : (nhq + nkk) * QK;  // the keys as projected are the values
     for (int idx = threadIdx.x; idx < nkv * VD; idx += blockDim.x) {
       const int g = idx / VD, d = idx - g * VD;
-      cache[(((size_t)page * nkv + g) * page_size + slot) * ROW + QK + d] =
+      cache[(((size_t)page * nkv + g) * page_size + slot) * ROW + KW + d] =
           from_float<T>(row[voff + idx] + (bias ? bias[voff + idx] : 0.f));
     }
   }
 }
 
+// With several maps a head the maps' outputs stay float32 (they are combined before anything rounds them).
+template <typename T> struct OutOf { using type = typename std::conditional<(MAPS > 1), float, T>::type; };
+
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
-attn_sink_simt_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ cache,
+attn_sink_simt_kernel(const T* __restrict__ q, typename OutOf<T>::type* __restrict__ out, const T* __restrict__ cache,
                       const int* __restrict__ token_seq, const int* __restrict__ positions,
                       const int* __restrict__ page_indptr, const int* __restrict__ page_ids,
                       const int* __restrict__ rows, const float* __restrict__ sinks, int nh, int nkv, int page_size,
-                      float scale, float softcap, int window, int num_pages, int* __restrict__ status,
+                      float scale, float softcap, int window, int keep_first, int num_pages, int* __restrict__ status,
                       const float* __restrict__ head_scale, const float* __restrict__ head_bias) {
+  using TO = typename OutOf<T>::type;
   __shared__ float qs[WARPS][QK];
   trigger_dependents();
   grid_dependency_wait();
@@ -179,11 +202,14 @@ attn_sink_simt_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __r
   const int* table = page_ids + page_indptr[s];
   int lo = 0;
   if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
+  // the positions kept in sight before the window: [0, kept)
+  const int kept = (window > 0 && keep_first > 0) ? min(keep_first, lo) : 0;
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
 
-  for (int gq = warp; gq < group; gq += WARPS) {
-    const int h = kvh * group + gq;
-    const T* qrow = q + ((size_t)t * nh + h) * QK;
+  for (int gq = warp; gq < group * MAPS; gq += WARPS) {
+    const int h = kvh * group * MAPS + gq;  // (head, map) counted as a query head
+    const int koff = (gq % MAPS) * QK;
+    const T* qrow = q + ((size_t)t * nh * MAPS + h) * QK;
     for (int d = lane; d < QK; d += 32) qs[warp][d] = to_float(qrow[d]);
     __syncwarp();
 
@@ -195,55 +221,91 @@ attn_sink_simt_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __r
 #pragma unroll
     for (int i = 0; i < DPL; i++) acc[i] = 0.f;
 
-    for (int base = lo; base <= p; base += 32) {
-      const int j = base + lane;
-      const bool live = j <= p;
-      long long rowoff = 0;
-      float sc = -FLT_MAX;
-      bool counted = false;
-      if (live) {
-        const int page = checked_page(table[j / page_size], num_pages, status);
-        if (page >= 0) {  // else: an id beyond the pool (the status flag is set); the key counts for nothing
-          rowoff = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * ROW;
-          sc = dot_key<T>(cache + rowoff, qs[warp]) * hscale;
-          if (softcap > 0.f) sc = softcap * tanhf(sc * inv_cap);
-          sc += hbias;
-          counted = true;
+    for (int seg = (kept > 0 ? 0 : 1); seg < 2; seg++) {
+      const int first = seg == 0 ? 0 : lo, last = seg == 0 ? kept - 1 : p;
+      for (int base = first; base <= last; base += 32) {
+        const int j = base + lane;
+        const bool live = j <= last;
+        long long rowoff = 0;
+        float sc = -FLT_MAX;
+        bool counted = false;
+        if (live) {
+          const int page = checked_page(table[j / page_size], num_pages, status);
+          if (page >= 0) {  // else: an id beyond the pool (the status flag is set); the key counts for nothing
+            rowoff = (((long long)page * nkv + kvh) * page_size + (j % page_size)) * ROW;
+            sc = dot_key<T>(cache + rowoff + koff, qs[warp]) * hscale;
+            if (softcap > 0.f) sc = softcap * tanhf(sc * inv_cap);
+            sc += hbias;
+            counted = true;
+          }
         }
-      }
-      float pj;
-      if constexpr (SIGMOID) {
-        pj = counted ? 1.f / (1.f + expf(-sc)) : 0.f;
-      } else {
-        const float bm = warp_max(sc);
-        const float m_new = fmaxf(m, bm);
-        const float alpha = expf(m - m_new);
-        pj = counted ? expf(sc - m_new) : 0.f;
-        l = l * alpha + warp_sum(pj);
-        m = m_new;
+        float pj;
+        if constexpr (SIGMOID) {
+          pj = counted ? 1.f / (1.f + expf(-sc)) : 0.f;
+        } else {
+          const float bm = warp_max(sc);
+          const float m_new = fmaxf(m, bm);
+          const float alpha = expf(m - m_new);
+          pj = counted ? expf(sc - m_new) : 0.f;
+          l = l * alpha + warp_sum(pj);
+          m = m_new;
 #pragma unroll
-        for (int i = 0; i < DPL; i++) acc[i] *= alpha;
-      }
-      const int nlive = (p - base + 1) < 32 ? (p - base + 1) : 32;
-      for (int jj = 0; jj < nlive; jj++) {
-        const float pv = __shfl_sync(0xffffffffu, pj, jj);
-        const long long ro = __shfl_sync(0xffffffffu, rowoff, jj);
-        const T* vrow = cache + ro + QK;
+          for (int i = 0; i < DPL; i++) acc[i] *= alpha;
+        }
+        const int nlive = (last - base + 1) < 32 ? (last - base + 1) : 32;
+        for (int jj = 0; jj < nlive; jj++) {
+          const float pv = __shfl_sync(0xffffffffu, pj, jj);
+          const long long ro = __shfl_sync(0xffffffffu, rowoff, jj);
+          const T* vrow = cache + ro + KW;
 #pragma unroll
-        for (int i = 0; i < DPL; i++) {
-          const int d = lane + 32 * i;
-          if (d < VD) acc[i] = fmaf(pv, to_float(vrow[d]), acc[i]);
+          for (int i = 0; i < DPL; i++) {
+            const int d = lane + 32 * i;
+            if (d < VD) acc[i] = fmaf(pv, to_float(vrow[d]), acc[i]);
+          }
         }
       }
     }
     const float inv_l = SIGMOID ? 1.f : (l > 0.f ? 1.f / l : 0.f);
-    T* orow = out + ((size_t)blockIdx.x * nh + h) * VD;
+    TO* orow = out + ((size_t)blockIdx.x * nh * MAPS + h) * VD;
 #pragma unroll
     for (int i = 0; i < DPL; i++) {
       const int d = lane + 32 * i;
-      if (d < VD) orow[d] = from_float<T>(acc[i] * inv_l);
+      if (d < VD) orow[d] = from_float<TO>(acc[i] * inv_l);
     }
     __syncwarp();
+  }
+}
+
+// The differential form's combination (two maps): a float32 [rows, heads, 2, VD];
+//   o = a_0 - lambda a_1,   out = o / sqrt(mean(o^2) + eps) * mult * sigmoid(gate[token][head])
+// gate: float32, row stride gate_stride, the heads' logits from column gate_off on (null: no gate); rows names the
+// tokens the rows of a belong to (null: row r is token r).  One warp a (row, head).
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+diff_combine_kernel(const float* __restrict__ a, const float* __restrict__ lambda, float eps, float mult,
+                    const float* __restrict__ gate, int gate_stride, int gate_off, const int* __restrict__ rows,
+                    T* __restrict__ out, int nh) {
+  trigger_dependents();
+  grid_dependency_wait();
+  const int r = blockIdx.x, lane = threadIdx.x & 31;
+  const float lam = lambda[0];
+  for (int h = threadIdx.x >> 5; h < nh; h += WARPS) {
+    const float* a0 = a + ((size_t)r * nh + h) * MAPS * VD;
+    float o[DPL], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; i++) {
+      const int d = lane + 32 * i;
+      o[i] = d < VD ? a0[d] - lam * a0[(MAPS > 1 ? VD : 0) + d] : 0.f;
+      ss = fmaf(o[i], o[i], ss);
+    }
+    ss = warp_sum(ss);
+    float f = rsqrtf(ss / (float)VD + eps) * mult;
+    if (gate != nullptr) f *= 1.f / (1.f + expf(-gate[(size_t)(rows ? rows[r] : r) * gate_stride + gate_off + h]));
+#pragma unroll
+    for (int i = 0; i < DPL; i++) {
+      const int d = lane + 32 * i;
+      if (d < VD) out[((size_t)r * nh + h) * VD + d] = from_float<T>(o[i] * f);
+    }
   }
 }
 
@@ -255,7 +317,7 @@ int prep_launch(const float* qkv, int stride, const float* bias, int unit_norm, 
   if (n_tokens <= 0) return 0;
   if (nkv <= 0 || nh <= 0 || nh % nkv != 0 || page_size <= 0) return -2;
   if (freq != nullptr && (rot_dims < 0 || rot_dims > QK || (rot_dims & 1))) return -2;
-  if (values_are_keys && QK != VD) return -2;
+  if (values_are_keys && (QK != VD || MAPS != 1)) return -2;
   return launch_pdl(sink_attn_prep_kernel<T>, dim3(n_tokens), dim3(256), 0, st, qkv, stride, bias, unit_norm, eps,
                     (T*)q_out, (T*)cache, positions, token_seq, page_indptr, page_ids, nh, nkv, page_size, num_pages,
                     write_cache, status, norm_w, freq, rot_dims, rot_pairs, values_are_keys);
@@ -264,14 +326,15 @@ int prep_launch(const float* qkv, int stride, const float* bias, int unit_norm, 
 template <typename T>
 int attn_launch(const void* q, void* out, const void* cache, const int* token_seq, const int* positions,
                 const int* page_indptr, const int* page_ids, const int* rows, int n_rows, const float* sinks, int nh,
-                int nkv, int page_size, float scale, float softcap, int window, int num_pages, int* status,
-                const float* head_scale, const float* head_bias, cudaStream_t st) {
+                int nkv, int page_size, float scale, float softcap, int window, int keep_first, int num_pages,
+                int* status, const float* head_scale, const float* head_bias, cudaStream_t st) {
   if (n_rows <= 0) return 0;
-  if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return -2;
+  if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || keep_first < 0) return -2;
   if (nkv > 65535) return -3;
-  return launch_pdl(attn_sink_simt_kernel<T>, dim3(n_rows, nkv), dim3(WARPS * 32), 0, st, (const T*)q, (T*)out,
-                    (const T*)cache, token_seq, positions, page_indptr, page_ids, rows, sinks, nh, nkv, page_size,
-                    scale, softcap, window, num_pages, status, head_scale, head_bias);
+  return launch_pdl(attn_sink_simt_kernel<T>, dim3(n_rows, nkv), dim3(WARPS * 32), 0, st, (const T*)q,
+                    (typename OutOf<T>::type*)out, (const T*)cache, token_seq, positions, page_indptr, page_ids, rows,
+                    sinks, nh, nkv, page_size, scale, softcap, window, keep_first, num_pages, status, head_scale,
+                    head_bias);
 }
 
 }  // namespace
@@ -290,11 +353,20 @@ int attn_launch(const void* q, void* out, const void* cache, const int* token_se
   TKB_EXPORT int tkb_attn_sink_simt_##SUF(const void* q, void* out, const void* cache, const int* token_seq,          \
                                           const int* positions, const int* page_indptr, const int* page_ids,          \
                                           const int* rows, int n_rows, const float* sinks, int nh, int nkv,           \
-                                          int page_size, float scale, float softcap, int window, int num_pages,       \
-                                          int* status, const float* head_scale, const float* head_bias, void* st) {   \
+                                          int page_size, float scale, float softcap, int window, int keep_first,      \
+                                          int num_pages, int* status, const float* head_scale,                        \
+                                          const float* head_bias, void* st) {                                         \
     return attn_launch<T>(q, out, cache, token_seq, positions, page_indptr, page_ids, rows, n_rows, sinks, nh, nkv,   \
-                          page_size, scale, softcap, window, num_pages, status, head_scale, head_bias,                \
+                          page_size, scale, softcap, window, keep_first, num_pages, status, head_scale, head_bias,    \
                           (cudaStream_t)st);                                                                          \
+  }                                                                                                                   \
+  TKB_EXPORT int tkb_diff_combine_##SUF(const float* a, const float* lambda, float eps, float mult,                   \
+                                        const float* gate, int gate_stride, int gate_off, const int* rows, void* out, \
+                                        int n_rows, int nh, void* st) {                                               \
+    if (n_rows <= 0) return 0;                                                                                        \
+    if (MAPS != 2 || nh <= 0) return -2;                                                                              \
+    return launch_pdl(diff_combine_kernel<T>, dim3(n_rows), dim3(WARPS * 32), 0, (cudaStream_t)st, a, lambda, eps,    \
+                      mult, gate, gate_stride, gate_off, rows, (T*)out, nh);                                          \
   }
 
 TKB_SINK_EXPORTS(f32, float)
@@ -391,12 +463,14 @@ __device__ __forceinline__ void stage_tile(bf16* buf, const bf16* __restrict__ c
 }
 
 // One warp, 16 rows, NT groups of 8 keys that start at row `kr0` of the staged tile (key index key0): scores, running
-// softmax, and the weighted sum of values.  lim_lo / lim_hi: the keys each of the thread's two rows may see.
+// softmax, and the weighted sum of values.  lim_lo / lim_hi: the keys each of the thread's two rows may see; keys
+// below `keep` are seen from below lim_lo too (the first positions that a window keeps).  koff: where the map's key
+// starts in a staged row.
 // MASKED false: every key of the span is seen by every row (the caller has checked), no limit is looked at.
 template <int NT, bool MASKED>
 __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const uint32_t (&qf)[KSTEPS][4], float (&o)[VT][4],
                                        float (&m)[2], float (&l)[2], const int (&lim_lo)[2], const int (&lim_hi)[2],
-                                       const ScoreMap (&sm)[2], int lane) {
+                                       const ScoreMap (&sm)[2], int lane, int koff = 0, int keep = 0) {
   const int g = lane >> 2, t = lane & 3;
   float sc[NT][4];
 #pragma unroll
@@ -404,7 +478,7 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
     sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
     if constexpr (KSTEPS % 2 == 0) {
       // four 8 x 8 pieces a load: keys nt * 8 .. + 7, key channels of two k-steps (a piece's row is one key's 8 channels)
-      const bf16* kp = buf + (kr0 + nt * 8 + (lane & 7)) * RS + (lane >> 3) * 8;
+      const bf16* kp = buf + (kr0 + nt * 8 + (lane & 7)) * RS + koff + (lane >> 3) * 8;
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ks += 2) {
         uint32_t b[4];
@@ -413,7 +487,7 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
         mma_bf16(sc[nt], qf[ks + 1], b[2], b[3]);
       }
     } else {
-      const bf16* krow = buf + (kr0 + nt * 8 + g) * RS + 2 * t;
+      const bf16* krow = buf + (kr0 + nt * 8 + g) * RS + koff + 2 * t;
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ks++) {
         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
@@ -433,7 +507,7 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
           float v = sigmoid2(mapped_score(sc[nt][h * 2 + e], sm[h]));
           if (MASKED) {
             const int key = key0 + nt * 8 + 2 * t + e;
-            if (key < lim_lo[h] || key > lim_hi[h]) v = 0.f;
+            if ((key < lim_lo[h] && key >= keep) || key > lim_hi[h]) v = 0.f;
           }
           sc[nt][h * 2 + e] = v;
         }
@@ -449,7 +523,7 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
         float v = mapped_score(sc[nt][h * 2 + e], sm[h]);
         if (MASKED) {
           const int key = key0 + nt * 8 + 2 * t + e;
-          if (key < lim_lo[h] || key > lim_hi[h]) v = -INFINITY;
+          if ((key < lim_lo[h] && key >= keep) || key > lim_hi[h]) v = -INFINITY;
         }
         sc[nt][h * 2 + e] = v;
         mx = fmaxf(mx, v);
@@ -482,7 +556,7 @@ __device__ __forceinline__ void attend(const bf16* buf, int kr0, int key0, const
   for (int kk = 0; kk < NT / 2; kk++) {  // 16 keys at a time
     uint32_t pf[4] = {pack_bf16(sc[2 * kk][0], sc[2 * kk][1]), pack_bf16(sc[2 * kk][2], sc[2 * kk][3]),
                       pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]), pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3])};
-    const bf16* vbase = buf + (kr0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + QK + (lane >> 4) * 8;
+    const bf16* vbase = buf + (kr0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + KW + (lane >> 4) * 8;
 #pragma unroll
     for (int vt = 0; vt < VT; vt += 2) {
       uint32_t b[4];
@@ -498,11 +572,11 @@ constexpr size_t TC_SMEM = (size_t)2 * KT * RS * sizeof(bf16);
 // Portions: blockIdx.y counts the 64-query tiles of the step's requests that bring more than one token from the end;
 // blockIdx.x is the query head.
 __global__ void __launch_bounds__(128)
-attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
+attn_sink_tiles_kernel(const bf16* __restrict__ q, OutOf<bf16>::type* __restrict__ out, const bf16* __restrict__ cache,
                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                        const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                        const int* __restrict__ page_ids, int n_seqs, const float* __restrict__ sinks, int nh, int nkv,
-                       int ps, float scale, float softcap, int window, int num_pages, int* __restrict__ status,
+                       int ps, float scale, float softcap, int window, int keep_first, int num_pages, int* __restrict__ status,
                        const float* __restrict__ head_scale, const float* __restrict__ head_bias) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* bufs = reinterpret_cast<bf16*>(smem_raw);
@@ -519,7 +593,8 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
   if (s >= n_seqs) return;
   grid_dependency_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  const int h = blockIdx.x, kvh = h / (nh / nkv);
+  // blockIdx.x counts (head, map) as query heads
+  const int h = blockIdx.x, kvh = (h / MAPS) / (nh / nkv), koff = (h % MAPS) * QK, nhm = nh * MAPS;
   const int n_q = seq_q_len[s], start = seq_q_start[s];
   const int pos0 = seq_kv_len[s] - n_q;  // position of the portion's first token
   const int r0 = tile * KT;              // first query of the tile within the portion
@@ -537,7 +612,7 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
     const int p = pos0 + r0 + r;
     lim_hi[hh] = live ? p : -1;
     lim_lo[hh] = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    const bf16* qrow = q + ((size_t)(start + r0 + (live ? r : 0)) * nh + h) * QK;
+    const bf16* qrow = q + ((size_t)(start + r0 + (live ? r : 0)) * nhm + h) * QK;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ks++) {
       qf[ks][hh] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
@@ -555,33 +630,47 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
 
   const int p_first = pos0 + r0, p_last = pos0 + r0 + rows - 1;
   const int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
-  const int n_tiles = (p_last - k_lo) / KT + 1;
-  // the keys this warp's rows can see: [w_lo, w_hi]
+  // the first positions that the window keeps in sight: [0, kept) lies before every row's window and is staged in
+  // tiles of its own, which come first; kept positions from k_lo on arrive with the window's tiles
+  const int keep = window > 0 ? keep_first : 0;
+  const int kept = min(keep, k_lo);
+  const int keep_tiles = (kept + KT - 1) / KT;
+  const int n_tiles = keep_tiles + (p_last - k_lo) / KT + 1;
+  auto tile_key0 = [&](int it) { return it < keep_tiles ? it * KT : k_lo + (it - keep_tiles) * KT; };
+  auto tile_first = [&](int it) { return it < keep_tiles ? 0 : k_lo; };
+  auto tile_last = [&](int it) { return it < keep_tiles ? kept - 1 : p_last; };
+  // the keys this warp's rows can see within the window's tiles: [w_lo, w_hi]
   const int w_first = pos0 + r0 + warp * 16;
-  const int w_lo = (window > 0 && w_first - window + 1 > 0) ? w_first - window + 1 : 0;
+  const int w_lo = keep > k_lo ? k_lo : ((window > 0 && w_first - window + 1 > 0) ? w_first - window + 1 : 0);
   const int w_hi = min(p_last, w_first + 15);
   const int w_last_lo = (window > 0 && w_first + 15 - window + 1 > 0) ? w_first + 15 - window + 1 : 0;  // the last row's
   bool bad = false;
-  stage_tile(bufs, cache, table, k_lo, k_lo, p_last, kvh, nkv, ps, num_pages, bad, tid);
+  stage_tile(bufs, cache, table, tile_key0(0), tile_first(0), tile_last(0), kvh, nkv, ps, num_pages, bad, tid);
   cp_async_commit();
   for (int it = 0; it < n_tiles; it++) {
     bf16* cur = bufs + (it & 1) * KT * RS;
     if (it + 1 < n_tiles) {
-      stage_tile(bufs + ((it + 1) & 1) * KT * RS, cache, table, k_lo + (it + 1) * KT, k_lo, p_last, kvh, nkv, ps, num_pages,
-                 bad, tid);
+      stage_tile(bufs + ((it + 1) & 1) * KT * RS, cache, table, tile_key0(it + 1), tile_first(it + 1), tile_last(it + 1), kvh,
+                 nkv, ps, num_pages, bad, tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    const int key0 = k_lo + it * KT;
-    if (warp * 16 < rows && key0 <= w_hi && key0 + KT - 1 >= w_lo) {  // warp-uniform: some row of the warp sees some key
+    const int key0 = tile_key0(it);
+    if (it < keep_tiles) {
+      // kept positions: every live row sees [0, kept), nothing beyond in this tile
+      if (warp * 16 < rows) {
+        const int kl[2] = {0, 0}, kh[2] = {lim_hi[0] < 0 ? -1 : kept - 1, lim_hi[1] < 0 ? -1 : kept - 1};
+        attend<8, true>(cur, 0, key0, qf, o, m, l, kl, kh, sm, lane, koff, 0);
+      }
+    } else if (warp * 16 < rows && key0 <= w_hi && key0 + KT - 1 >= w_lo) {  // warp-uniform: some row of the warp sees some key
       // all 16 rows live and the whole tile inside every row's window and before the warp's first query: no masks
       if (warp * 16 + 16 <= rows && key0 + KT - 1 <= w_first && key0 >= w_last_lo)
-        attend<8, false>(cur, 0, key0, qf, o, m, l, lim_lo, lim_hi, sm, lane);
+        attend<8, false>(cur, 0, key0, qf, o, m, l, lim_lo, lim_hi, sm, lane, koff, keep);
       else
-        attend<8, true>(cur, 0, key0, qf, o, m, l, lim_lo, lim_hi, sm, lane);
+        attend<8, true>(cur, 0, key0, qf, o, m, l, lim_lo, lim_hi, sm, lane, koff, keep);
     }
     __syncthreads();  // the buffer is free for the tile after next
   }
@@ -593,23 +682,27 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const
     const int r = warp * 16 + g + hh * 8;
     if (r < rows) {
       const float inv = l[hh] > 0.f ? 1.f / l[hh] : 0.f;
-      bf16* orow = out + ((size_t)(start + r0 + r) * nh + h) * VD + 2 * t;
+      auto* orow = out + ((size_t)(start + r0 + r) * nhm + h) * VD + 2 * t;
 #pragma unroll
-      for (int vt = 0; vt < VT; vt++)
-        *reinterpret_cast<uint32_t*>(orow + vt * 8) = pack_bf16(o[vt][hh * 2] * inv, o[vt][hh * 2 + 1] * inv);
+      for (int vt = 0; vt < VT; vt++) {
+        if constexpr (MAPS > 1)
+          *reinterpret_cast<float2*>(orow + vt * 8) = make_float2(o[vt][hh * 2] * inv, o[vt][hh * 2 + 1] * inv);
+        else
+          *reinterpret_cast<uint32_t*>(orow + vt * 8) = pack_bf16(o[vt][hh * 2] * inv, o[vt][hh * 2 + 1] * inv);
+      }
     }
   }
 }
 
-// Single tokens: blockIdx.x = request row (it leaves unless the request brings one token), blockIdx.y = key/value
-// head * head tiles + head tile (16 query heads a tile).
+// Single tokens: blockIdx.x = request row (it leaves unless the request brings one token), blockIdx.y = ((key/value
+// head * MAPS) + map) * head tiles + head tile (16 query heads a tile).
 __global__ void __launch_bounds__(128)
-attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
+attn_sink_single_kernel(const bf16* __restrict__ q, OutOf<bf16>::type* __restrict__ out, const bf16* __restrict__ cache,
                         const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
                         const int* __restrict__ seq_kv_len, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_ids, const float* __restrict__ sinks, int nh, int nkv, int head_tiles,
-                        int ps, float scale, float softcap, int window, int num_pages, int* __restrict__ status,
-                        float* __restrict__ part, const float* __restrict__ head_scale,
+                        int ps, float scale, float softcap, int window, int keep_first, int num_pages,
+                        int* __restrict__ status, float* __restrict__ part, const float* __restrict__ head_scale,
                         const float* __restrict__ head_bias) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* bufs = reinterpret_cast<bf16*>(smem_raw);
@@ -620,7 +713,8 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
   grid_dependency_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int group = nh / nkv;
-  const int kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y - kvh * head_tiles) * 16;
+  const int km = blockIdx.y / head_tiles, g0 = (blockIdx.y - km * head_tiles) * 16;
+  const int kvh = km / MAPS, map = km % MAPS, koff = map * QK, nhm = nh * MAPS;
   const int gn = min(16, group - g0);
   const int tok = seq_q_start[s];
   const int p = seq_kv_len[s] - 1;
@@ -629,14 +723,13 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
   const int k_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
 
   uint32_t qf[KSTEPS][4];
-  int lim_lo[2] = {k_lo, k_lo}, lim_hi[2] = {p, p};
   float m[2], l[2];
 #pragma unroll
   for (int hh = 0; hh < 2; hh++) {
     const int r = g + hh * 8;
     const bool live = r < gn;
-    const int head = kvh * group + g0 + (live ? r : 0);
-    const bf16* qrow = q + ((size_t)tok * nh + head) * QK;
+    const int head = (kvh * group + g0 + (live ? r : 0)) * MAPS + map;  // (head, map) counted as a query head
+    const bf16* qrow = q + ((size_t)tok * nhm + head) * QK;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ks++) {
       qf[ks][hh] = live ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
@@ -651,27 +744,38 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
 #pragma unroll
   for (int vt = 0; vt < VT; vt++) o[vt][0] = o[vt][1] = o[vt][2] = o[vt][3] = 0.f;
 
-  // the request's tiles are shared out evenly among the splits (blockIdx.z); a split may be left without any
-  const int all_tiles = (p - k_lo) / KT + 1;
+  // the request's tiles are shared out evenly among the splits (blockIdx.z); a split may be left without any.  The
+  // first positions that the window keeps in sight, [0, kept), have tiles of their own, which come first.
+  const int kept = window > 0 ? min(keep_first, k_lo) : 0;
+  const int keep_tiles = (kept + KT - 1) / KT;
+  const int all_tiles = keep_tiles + (p - k_lo) / KT + 1;
   const int per_split = (all_tiles + splits - 1) / splits;
   const int it0 = split * per_split;
   const int n_tiles = min(all_tiles, it0 + per_split) - it0;
+  auto tile_key0 = [&](int it) { return it < keep_tiles ? it * KT : k_lo + (it - keep_tiles) * KT; };
+  auto tile_first = [&](int it) { return it < keep_tiles ? 0 : k_lo; };
+  auto tile_last = [&](int it) { return it < keep_tiles ? kept - 1 : p; };
   bool bad = false;
-  if (n_tiles > 0) stage_tile(bufs, cache, table, k_lo + it0 * KT, k_lo, p, kvh, nkv, ps, num_pages, bad, tid);
+  if (n_tiles > 0)
+    stage_tile(bufs, cache, table, tile_key0(it0), tile_first(it0), tile_last(it0), kvh, nkv, ps, num_pages, bad, tid);
   cp_async_commit();
   for (int it = 0; it < n_tiles; it++) {
     bf16* cur = bufs + (it & 1) * KT * RS;
     if (it + 1 < n_tiles) {
-      stage_tile(bufs + ((it + 1) & 1) * KT * RS, cache, table, k_lo + (it0 + it + 1) * KT, k_lo, p, kvh, nkv, ps, num_pages, bad,
-                 tid);
+      stage_tile(bufs + ((it + 1) & 1) * KT * RS, cache, table, tile_key0(it0 + it + 1), tile_first(it0 + it + 1),
+                 tile_last(it0 + it + 1), kvh, nkv, ps, num_pages, bad, tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    const int key0 = k_lo + (it0 + it) * KT + warp * 16;
-    if (key0 <= p) attend<2, true>(cur, warp * 16, key0, qf, o, m, l, lim_lo, lim_hi, sm, lane);
+    const int key0 = tile_key0(it0 + it) + warp * 16;
+    const int last = tile_last(it0 + it);
+    if (key0 <= last) {
+      const int tl[2] = {tile_first(it0 + it), tile_first(it0 + it)}, th[2] = {last, last};
+      attend<2, true>(cur, warp * 16, key0, qf, o, m, l, tl, th, sm, lane, koff, 0);
+    }
     __syncthreads();
   }
   cp_async_wait<0>();
@@ -711,11 +815,11 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
       acc += f * so[(w * 16 + r) * SO + d];
       ll += f * sml[(w * 16 + r) * 2 + 1];
     }
-    const int head = kvh * group + g0 + r;
+    const int head = (kvh * group + g0 + r) * MAPS + map;
     if (splits == 1) {
-      out[((size_t)tok * nh + head) * VD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+      out[((size_t)tok * nhm + head) * VD + d] = from_float<OutOf<bf16>::type>(ll > 0.f ? acc / ll : 0.f);
     } else {  // this split's share: sums relative to its own maximum, for attn_sink_merge
-      float* pr = part + (((size_t)s * nh + head) * splits + split) * (VD + 2);
+      float* pr = part + (((size_t)s * nhm + head) * splits + split) * (VD + 2);
       pr[d] = acc;
       if (d == 0) {
         pr[VD] = mm;
@@ -726,7 +830,7 @@ attn_sink_single_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, cons
 }
 
 // The splits of every single-token request put together: grid (request row, query head).
-__global__ void attn_sink_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out,
+__global__ void attn_sink_merge_kernel(const float* __restrict__ part, OutOf<bf16>::type* __restrict__ out,
                                        const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len, int nh,
                                        int splits) {
   trigger_dependents();
@@ -742,7 +846,7 @@ __global__ void attn_sink_merge_kernel(const float* __restrict__ part, bf16* __r
   for (int d = threadIdx.x; d < VD; d += blockDim.x) {
     float acc = 0.f;
     for (int z = 0; z < splits; z++) acc += exp2f(pr[z * (VD + 2) + VD] - mm) * pr[z * (VD + 2) + d];
-    out[((size_t)seq_q_start[s] * nh + head) * VD + d] = __float2bfloat16_rn(acc * inv);
+    out[((size_t)seq_q_start[s] * nh + head) * VD + d] = from_float<OutOf<bf16>::type>(acc * inv);
   }
 }
 
@@ -756,12 +860,13 @@ TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache
                                      const int* seq_q_len, const int* seq_kv_len, const int* page_indptr,
                                      const int* page_ids, int n_tokens, int n_seqs, int portions, int singles,
                                      const float* sinks, int nh, int nkv, int page_size, float scale, float softcap,
-                                     int window, int num_pages, int* status, float* part, int splits,
+                                     int window, int keep_first, int num_pages, int* status, float* part, int splits,
                                      const float* head_scale, const float* head_bias, void* st) {
+  using TO = OutOf<bf16>::type;
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
-  if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return -2;
+  if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || keep_first < 0) return -2;
   const int head_tiles = (nh / nkv + 15) / 16;
-  if (nh > 65535 || nkv * head_tiles > 65535) return -3;
+  if (nh * MAPS > 65535 || nkv * MAPS * head_tiles > 65535) return -3;
   if (TC_SMEM > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attn_sink_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
     if (e == cudaSuccess)
@@ -772,20 +877,21 @@ TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache
   if (splits < 1 || part == nullptr) splits = 1;
   if (splits > 64) return -2;
   if (singles) {
-    rc = launch_pdl(attn_sink_single_kernel, dim3(n_seqs, nkv * head_tiles, splits), dim3(128), TC_SMEM, (cudaStream_t)st,
-                    (const bf16*)q, (bf16*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr,
-                    page_ids, sinks, nh, nkv, head_tiles, page_size, scale, softcap, window, num_pages, status, part,
-                    head_scale, head_bias);
+    rc = launch_pdl(attn_sink_single_kernel, dim3(n_seqs, nkv * MAPS * head_tiles, splits), dim3(128), TC_SMEM,
+                    (cudaStream_t)st, (const bf16*)q, (TO*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len,
+                    page_indptr, page_ids, sinks, nh, nkv, head_tiles, page_size, scale, softcap, window, keep_first,
+                    num_pages, status, part, head_scale, head_bias);
     if (rc == 0 && splits > 1)
-      rc = launch_pdl(attn_sink_merge_kernel, dim3(n_seqs, nh), dim3(VD >= 128 ? 128 : 64), 0, (cudaStream_t)st,
-                      (const float*)part, (bf16*)out, seq_q_start, seq_q_len, nh, splits);
+      rc = launch_pdl(attn_sink_merge_kernel, dim3(n_seqs, nh * MAPS), dim3(VD >= 128 ? 128 : 64), 0, (cudaStream_t)st,
+                      (const float*)part, (TO*)out, seq_q_start, seq_q_len, nh * MAPS, splits);
   }
   if (rc != 0 || !portions) return rc;
   const int tiles = n_tokens / KT + n_seqs;  // no step of this shape has more 64-query tiles
   if (tiles > 65535) return -3;
-  return launch_pdl(attn_sink_tiles_kernel, dim3(nh, tiles), dim3(128), TC_SMEM, (cudaStream_t)st, (const bf16*)q,
-                    (bf16*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, n_seqs,
-                    sinks, nh, nkv, page_size, scale, softcap, window, num_pages, status, head_scale, head_bias);
+  return launch_pdl(attn_sink_tiles_kernel, dim3(nh * MAPS, tiles), dim3(128), TC_SMEM, (cudaStream_t)st, (const bf16*)q,
+                    (TO*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, n_seqs,
+                    sinks, nh, nkv, page_size, scale, softcap, window, keep_first, num_pages, status, head_scale,
+                    head_bias);
 }
 #endif  // tensor-core sizes
 TKB_EXPORT int tkb_attn_sink_has_tc() {

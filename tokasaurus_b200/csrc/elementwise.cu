@@ -730,7 +730,12 @@ TKB_EXPORT int tkb_rope_kv_write_partials_bf16(const float* partials, int n_part
 // interleave == 0: gate columns first, then up columns.  interleave == 8: columns come in groups of 16, the
 // 8 gate columns of features 8j..8j+7 followed by their 8 up columns (the layout the small-batch
 // matrix product wants for its fused epilogue).
-template <typename T>
+// ACT 0: silu(gate) * up.  ACT 1: gelu_tanh(gate) * up, the tanh form 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))).
+template <int ACT> __device__ __forceinline__ float gate_act(float g) {
+  if constexpr (ACT == 0) return g / (1.f + expf(-g));
+  else return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+template <typename T, int ACT>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I,
                                 int interleave) {
   trigger_dependents();
@@ -750,10 +755,10 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
       for (int h = 0; h < 2; h++) {
         const float4 g = load4(row + gc + 4 * h), u = load4(row + uc + 4 * h);
         float4 r;
-        r.x = g.x / (1.f + expf(-g.x)) * u.x;
-        r.y = g.y / (1.f + expf(-g.y)) * u.y;
-        r.z = g.z / (1.f + expf(-g.z)) * u.z;
-        r.w = g.w / (1.f + expf(-g.w)) * u.w;
+        r.x = gate_act<ACT>(g.x) * u.x;
+        r.y = gate_act<ACT>(g.y) * u.y;
+        r.z = gate_act<ACT>(g.z) * u.z;
+        r.w = gate_act<ACT>(g.w) * u.w;
         store4(out + t * I + i + 4 * h, r);
       }
     }
@@ -767,11 +772,11 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
     const int uc = interleave ? gc + 8 : I + i;
     const float g = to_float(gu[t * 2 * I + gc]);
     const float u = to_float(gu[t * 2 * I + uc]);
-    const float sg = g / (1.f + expf(-g));
+    const float sg = gate_act<ACT>(g);
     out[idx] = from_float<T>(sg * u);
   }
 }
-template <typename T>
+template <typename T, int ACT = 0>
 static int silu_mul_launch(const void* gu, void* out, int rows, int I, int interleave, cudaStream_t st) {
   if (interleave != 0 && (interleave != 8 || (I & 7))) return -2;
   long long total = (long long)rows * I;
@@ -779,13 +784,19 @@ static int silu_mul_launch(const void* gu, void* out, int rows, int I, int inter
   long long blocks = (((I & 7) == 0 ? total / 8 : total) + 255) / 256;
   if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   if (blocks < 1) blocks = 1;
-  return launch_pdl(silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, st, (const T*)gu, (T*)out, total, I, interleave);
+  return launch_pdl(silu_mul_kernel<T, ACT>, dim3((int)blocks), dim3(256), 0, st, (const T*)gu, (T*)out, total, I, interleave);
 }
 TKB_EXPORT int tkb_silu_mul_f32(const void* gu, void* out, int rows, int I, int interleave, void* st) {
   return silu_mul_launch<float>(gu, out, rows, I, interleave, (cudaStream_t)st);
 }
 TKB_EXPORT int tkb_silu_mul_bf16(const void* gu, void* out, int rows, int I, int interleave, void* st) {
   return silu_mul_launch<__nv_bfloat16>(gu, out, rows, I, interleave, (cudaStream_t)st);
+}
+TKB_EXPORT int tkb_gelu_tanh_mul_f32(const void* gu, void* out, int rows, int I, int interleave, void* st) {
+  return silu_mul_launch<float, 1>(gu, out, rows, I, interleave, (cudaStream_t)st);
+}
+TKB_EXPORT int tkb_gelu_tanh_mul_bf16(const void* gu, void* out, int rows, int I, int interleave, void* st) {
+  return silu_mul_launch<__nv_bfloat16, 1>(gu, out, rows, I, interleave, (cudaStream_t)st);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -298,3 +298,18 @@ TKB_EXPORT int tkb_gemm_tcgen05_grouped_bf16(const void* A, int lda, const void*
   return gated ? launch<128, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups)
                : launch<128, false>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups, 0.f, 0.f, plain_act);
 }
+
+// The grouped gated form with the clamped unit in its epilogue (see tkb_gemm_tcgen05_clamped_bf16): every group's rows
+// interleave gate and up.
+TKB_EXPORT int tkb_gemm_tcgen05_grouped_clamped_bf16(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
+                                                     int M, int N, int K, float limit, float alpha,
+                                                     const int* tile_group, int groups, int* status, void* st_) {
+  cudaStream_t st = (cudaStream_t)st_;
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return -2;
+  if (groups <= 0 || tile_group == nullptr || (N & 15) || !(limit > 0.f)) return -2;
+  int rc = get_encode();
+  if (rc) return rc;
+  if (N >= 256) return launch<256, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups, limit, alpha);
+  return launch<128, true>(A, lda, W, ldw, out, ldo, M, N, K, status, st, tile_group, groups, limit, alpha);
+}

@@ -9,6 +9,11 @@
 // itself on the FP32 pipes for any mix of prompt portions and single tokens (scores, softmax weights and sums
 // float32).  Each is built for float and bfloat16 activations.
 //
+// Both rotations also come in the other pairing (halves: channel i with channel i + rot_dims / 2), with frequencies
+// given in float64 (freq64: the angle, its sine and cosine are then made in float64, once a token) and with a factor
+// `mag` on every sine and cosine (a frequency-scaling scheme's attention factor).  head_sigmoid_gate multiplies every
+// head's output by the sigmoid of a per-token, per-head logit (an output gate).
+//
 // Compile with -DTKB_LAT_RANK=<rank of the latent>.
 #include "common.cuh"
 #include <float.h>
@@ -39,7 +44,7 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int stride, i
                                    T* __restrict__ cache, const int* __restrict__ positions,
                                    const int* __restrict__ token_seq, const int* __restrict__ page_indptr,
                                    const int* __restrict__ page_ids, int page_size, int num_pages, float eps,
-                                   int* __restrict__ status) {
+                                   int* __restrict__ status, const double* __restrict__ freq64, int halves, float mag) {
   __shared__ float scratch[33];
   trigger_dependents();
   grid_dependency_wait();
@@ -67,42 +72,81 @@ __global__ void latent_prep_kernel(const float* __restrict__ proj, int stride, i
   T* dst = cache + ((size_t)page * page_size + (p % page_size)) * (RANK + rot);
   for (int i = threadIdx.x; i < RANK; i += blockDim.x) dst[i] = from_float<T>(row[kv_off + i] * r * kv_w[i]);
   const float* kr = row + kv_off + RANK;
-  for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
+  const int half = rot_dims / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float sn, cs;
-    sincosf((float)p * inv_freq[i], &sn, &cs);
-    const float u = kr[2 * i], v = kr[2 * i + 1];
-    dst[RANK + 2 * i] = from_float<T>(u * cs - v * sn);
-    dst[RANK + 2 * i + 1] = from_float<T>(v * cs + u * sn);
+    if (freq64 != nullptr) {
+      double s64, c64;
+      sincos((double)p * freq64[i], &s64, &c64);
+      sn = (float)s64 * mag;
+      cs = (float)c64 * mag;
+    } else {
+      sincosf((float)p * inv_freq[i], &sn, &cs);
+    }
+    const int a = halves ? i : 2 * i, b = halves ? i + half : 2 * i + 1;
+    const float u = kr[a], v = kr[b];
+    dst[RANK + a] = from_float<T>(u * cs - v * sn);
+    dst[RANK + b] = from_float<T>(v * cs + u * sn);
   }
   for (int i = rot_dims + threadIdx.x; i < rot; i += blockDim.x) dst[RANK + i] = from_float<T>(kr[i]);
 }
 
 // dst[t][head][dst_off + i] = rotated src[t][head][src_off + i], i < rot: the pairs (2i, 2i+1), i < rot_dims / 2, are
 // turned by position * inv_freq[i], the values from rot_dims on pass unchanged.  dst may be src (in place).
+constexpr int ROT_TABLE = 256;  // most rotated pairs of a head
+
 template <typename T>
 __global__ void rotate_pairs_kernel(const T* __restrict__ src, int src_token_stride, int src_head_stride, int src_off,
                                     T* __restrict__ dst, int dst_token_stride, int dst_head_stride, int dst_off,
                                     int n_heads, int rot, int rot_dims, const float* __restrict__ inv_freq,
-                                    const int* __restrict__ positions, const int* __restrict__ token_seq) {
+                                    const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                    const double* __restrict__ freq64, int halves, float mag) {
+  __shared__ float tcs[ROT_TABLE], tsn[ROT_TABLE];
   trigger_dependents();
   grid_dependency_wait();
   const int t = blockIdx.x;
   if (token_seq[t] < 0) return;
-  const float p = (float)positions[t];
   const int half = rot_dims / 2, per_head = half + (rot - rot_dims);
+  // the token's cosines and sines once, for all heads
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    if (freq64 != nullptr) {
+      double s64, c64;
+      sincos((double)positions[t] * freq64[i], &s64, &c64);
+      tsn[i] = (float)s64 * mag;
+      tcs[i] = (float)c64 * mag;
+    } else {
+      sincosf((float)positions[t] * inv_freq[i], &tsn[i], &tcs[i]);
+    }
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < n_heads * per_head; idx += blockDim.x) {
     const int h = idx / per_head, i = idx - h * per_head;
     const T* q = src + (size_t)t * src_token_stride + (size_t)h * src_head_stride + src_off;
     T* o = dst + (size_t)t * dst_token_stride + (size_t)h * dst_head_stride + dst_off;
     if (i < half) {
-      float sn, cs;
-      sincosf(p * inv_freq[i], &sn, &cs);
-      const float u = to_float(q[2 * i]), v = to_float(q[2 * i + 1]);
-      o[2 * i] = from_float<T>(u * cs - v * sn);
-      o[2 * i + 1] = from_float<T>(v * cs + u * sn);
+      const int a = halves ? i : 2 * i, b = halves ? i + half : 2 * i + 1;
+      const float sn = tsn[i], cs = tcs[i];
+      const float u = to_float(q[a]), v = to_float(q[b]);
+      o[a] = from_float<T>(u * cs - v * sn);
+      o[b] = from_float<T>(v * cs + u * sn);
     } else {
       o[rot_dims + i - half] = q[rot_dims + i - half];
     }
+  }
+}
+
+// val[r][h][:] *= sigmoid(gate[token(r)][gate_off + h]): an output gate, one number a (token, head); gate float32 with
+// row stride gate_stride; rows names the tokens that val's rows belong to (null: row r is token r).  One block a row.
+template <typename T>
+__global__ void head_sigmoid_gate_kernel(T* __restrict__ val, const float* __restrict__ gate, int gate_stride,
+                                         int gate_off, const int* __restrict__ rows, int n_heads, int vdim) {
+  trigger_dependents();
+  grid_dependency_wait();
+  const int r = blockIdx.x;
+  const float* g = gate + (size_t)(rows ? rows[r] : r) * gate_stride + gate_off;
+  for (int idx = threadIdx.x; idx < n_heads * vdim; idx += blockDim.x) {
+    const float f = 1.f / (1.f + expf(-g[idx / vdim]));
+    val[(size_t)r * n_heads * vdim + idx] = from_float<T>(to_float(val[(size_t)r * n_heads * vdim + idx]) * f);
   }
 }
 
@@ -231,22 +275,23 @@ template <typename T>
 int prep_launch(const float* proj, int stride, int q_off, int q_rank, const float* q_w, void* cq_out, int kv_off,
                 int rot, int rot_dims, const float* kv_w, const float* inv_freq, void* cache, const int* positions,
                 const int* token_seq, const int* page_indptr, const int* page_ids, int page_size, int num_pages,
-                float eps, int n_tokens, int* status, cudaStream_t st) {
+                float eps, int n_tokens, int* status, const double* freq64, int halves, float mag, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (rot_dims < 0 || rot_dims > rot || rot_dims % 2 || page_size <= 0) return -2;
   return launch_pdl(latent_prep_kernel<T>, dim3(n_tokens), dim3(128), 0, st, proj, stride, q_off, q_rank, q_w,
                     (T*)cq_out, kv_off, rot, rot_dims, kv_w, inv_freq, (T*)cache, positions, token_seq, page_indptr,
-                    page_ids, page_size, num_pages, eps, status);
+                    page_ids, page_size, num_pages, eps, status, freq64, halves, mag);
 }
 
 template <typename T>
 int rotate_launch(const void* src, int src_ts, int src_hs, int src_off, void* dst, int dst_ts, int dst_hs, int dst_off,
                   int n_heads, int rot, int rot_dims, const float* inv_freq, const int* positions, const int* token_seq,
-                  int n_tokens, cudaStream_t st) {
+                  int n_tokens, const double* freq64, int halves, float mag, cudaStream_t st) {
   if (n_tokens <= 0 || rot <= 0) return 0;
-  if (rot_dims % 2 || rot_dims > rot) return -2;
+  if (rot_dims % 2 || rot_dims > rot || rot_dims / 2 > ROT_TABLE) return -2;
   return launch_pdl(rotate_pairs_kernel<T>, dim3(n_tokens), dim3(128), 0, st, (const T*)src, src_ts, src_hs, src_off,
-                    (T*)dst, dst_ts, dst_hs, dst_off, n_heads, rot, rot_dims, inv_freq, positions, token_seq);
+                    (T*)dst, dst_ts, dst_hs, dst_off, n_heads, rot, rot_dims, inv_freq, positions, token_seq, freq64,
+                    halves, mag);
 }
 
 template <typename T>
@@ -275,17 +320,25 @@ int attn_launch(const void* q_abs, long long qa_ts, long long qa_hs, const void*
                                        void* cq_out, int kv_off, int rot, int rot_dims, const float* kv_w,             \
                                        const float* inv_freq, void* cache, const int* positions, const int* token_seq, \
                                        const int* page_indptr, const int* page_ids, int page_size, int num_pages,      \
-                                       float eps, int n_tokens, int* status, void* st) {                               \
+                                       float eps, int n_tokens, int* status, const double* freq64, int halves,         \
+                                       float mag, void* st) {                                                          \
     return prep_launch<T>(proj, stride, q_off, q_rank, q_w, cq_out, kv_off, rot, rot_dims, kv_w, inv_freq, cache,      \
                           positions, token_seq, page_indptr, page_ids, page_size, num_pages, eps, n_tokens, status,    \
-                          (cudaStream_t)st);                                                                           \
+                          freq64, halves, mag, (cudaStream_t)st);                                                      \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_head_sigmoid_gate_##SUF(void* val, const float* gate, int gate_stride, int gate_off,              \
+                                             const int* rows, int n_rows, int n_heads, int vdim, void* st) {           \
+    if (n_rows <= 0) return 0;                                                                                         \
+    if (n_heads <= 0 || vdim <= 0) return -2;                                                                          \
+    return launch_pdl(head_sigmoid_gate_kernel<T>, dim3(n_rows), dim3(256), 0, (cudaStream_t)st, (T*)val, gate,        \
+                      gate_stride, gate_off, rows, n_heads, vdim);                                                     \
   }                                                                                                                    \
   TKB_EXPORT int tkb_rotate_pairs_##SUF(const void* src, int src_ts, int src_hs, int src_off, void* dst, int dst_ts,    \
                                         int dst_hs, int dst_off, int n_heads, int rot, int rot_dims,                   \
                                         const float* inv_freq, const int* positions, const int* token_seq,             \
-                                        int n_tokens, void* st) {                                                      \
+                                        int n_tokens, const double* freq64, int halves, float mag, void* st) {         \
     return rotate_launch<T>(src, src_ts, src_hs, src_off, dst, dst_ts, dst_hs, dst_off, n_heads, rot, rot_dims,        \
-                            inv_freq, positions, token_seq, n_tokens, (cudaStream_t)st);                               \
+                            inv_freq, positions, token_seq, n_tokens, freq64, halves, mag, (cudaStream_t)st);          \
   }                                                                                                                    \
   TKB_EXPORT int tkb_latent_attn_simt_##SUF(const void* q_abs, long long qa_ts, long long qa_hs, const void* q_rot,    \
                                             long long qr_ts, long long qr_hs, int rot, void* out, const void* cache,   \

@@ -82,10 +82,11 @@ moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ wr, const f
 }
 
 // Router, second kernel: one warp a token takes the `top` largest logits one after the other (equal logits: the
-// lower expert first); weights = softmax over the chosen logits.  Rows of padding tokens choose nothing.
+// lower expert first); weights = softmax over the chosen logits, or (over_all) the chosen experts' shares of the
+// softmax over ALL experts, not renormalised; both times a number `scale`.  Rows of padding tokens choose nothing.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_choose_kernel(const float* __restrict__ z_all, const int* __restrict__ token_seq, int* __restrict__ top_idx,
-                  float* __restrict__ top_w, int n_tokens, int E, int top) {
+                  float* __restrict__ top_w, int n_tokens, int E, int top, int over_all, float scale) {
   extern __shared__ float zs[];  // [warps][E]
   trigger_dependents();
   grid_dependency_wait();
@@ -102,7 +103,14 @@ moe_choose_kernel(const float* __restrict__ z_all, const int* __restrict__ token
   float* z = zs + (size_t)warp * E;
   for (int e = lane; e < E; e += 32) z[e] = z_all[(size_t)t * E + e];
   __syncwarp();
-  float first = 0.f, denom = 0.f;
+  float first = 0.f, denom = 0.f, all = 0.f;
+  if (over_all) {  // the sum of exp(z - max) over every expert, before the choice overwrites what it takes
+    float mx = -FLT_MAX;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    for (int e = lane; e < E; e += 32) all += expf(z[e] - mx);
+    all = warp_sum(all);
+  }
   for (int k = 0; k < top; k++) {
     float best = -FLT_MAX;
     int arg = 0x7fffffff;
@@ -126,7 +134,7 @@ moe_choose_kernel(const float* __restrict__ z_all, const int* __restrict__ token
     }
     __syncwarp();
   }
-  const float inv = 1.f / denom;
+  const float inv = scale / (over_all ? all : denom);
   __syncwarp();
   for (int k = lane; k < top; k += 32) top_w[(size_t)t * top + k] *= inv;
 }
@@ -301,14 +309,20 @@ __global__ void moe_gather_kernel(const T* __restrict__ src, const int* __restri
 // src(p) = order[p] / top if `order` is given (rows of the step's tokens), else p.  Block (x, y): column tile x of the
 // y-th row tile, counted over the experts' spans in turn; blocks beyond the last tile leave at once.
 constexpr int BM = 64, BN = 64, BK = 16;
-constexpr int ACT_NONE = 0, ACT_GATED = 1, ACT_GELU = 2;
+constexpr int ACT_NONE = 0, ACT_GATED = 1, ACT_GELU = 2, ACT_CLAMPED = 3;
+// the clamped gated unit: g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(alpha g) * (u + 1)
+__device__ __forceinline__ float clamped_unit(float gate, float up, float limit, float alpha) {
+  const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+  return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
 __device__ __forceinline__ float gelu_erf_f(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
 
 template <typename TA, typename TC, int ACT>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC* __restrict__ C, int ldc,
-                const int* __restrict__ offsets, const int* __restrict__ order, int top, int E, int N, int K) {
-  constexpr bool GATED = ACT == ACT_GATED;
+                const int* __restrict__ offsets, const int* __restrict__ order, int top, int E, int N, int K,
+                float limit, float alpha) {
+  constexpr bool GATED = ACT == ACT_GATED || ACT == ACT_CLAMPED;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   __shared__ float Us[GATED ? BK : 1][BN + 4];
@@ -385,7 +399,8 @@ moe_gemm_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC*
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
       float v = acc[i][j];
-      if (GATED) v = v / (1.f + expf(-v)) * acu[i][j];
+      if (ACT == ACT_CLAMPED) v = clamped_unit(v, acu[i][j], limit, alpha);
+      else if (GATED) v = v / (1.f + expf(-v)) * acu[i][j];
       if (ACT == ACT_GELU) v = gelu_erf_f(v);
       C[(size_t)p * ldc + n] = from_float<TC>(v);
     }
@@ -424,8 +439,9 @@ template <> struct Vec8<float> {
 template <typename TA, typename TC, int ACT>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 moe_gemv_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC* __restrict__ C, int ldc,
-                const int* __restrict__ offsets, const int* __restrict__ order, int top, int N, int K) {
-  constexpr bool GATED = ACT == ACT_GATED;
+                const int* __restrict__ offsets, const int* __restrict__ order, int top, int N, int K, float limit,
+                float alpha) {
+  constexpr bool GATED = ACT == ACT_GATED || ACT == ACT_CLAMPED;
   trigger_dependents();
   grid_dependency_wait();
   const int e = blockIdx.y;
@@ -485,7 +501,7 @@ moe_gemv_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC*
             float v = warp_sum(acc[j][r]);
             if (GATED) {
               const float u = warp_sum(acu[j][r]);
-              v = v / (1.f + expf(-v)) * u;
+              v = ACT == ACT_CLAMPED ? clamped_unit(v, u, limit, alpha) : v / (1.f + expf(-v)) * u;
             }
             if (ACT == ACT_GELU) v = gelu_erf_f(v);
             const int f = f0 + j;
@@ -498,30 +514,38 @@ moe_gemv_kernel(const TA* __restrict__ A, int lda, const TA* __restrict__ W, TC*
 }
 
 // out[t] = sum_k top_w[t, k] * y[place_of[t * top + k]]  (+ shared[t]), in choice order, float32 sums, rounded once.
-// shared: [rows, H] in the activation type, or float32 slices [n_slices][rows, H] added in slice order.
+// shared: [rows, H] in the activation type, or float32 slices [n_slices][rows, H] added in slice order; shared_gate
+// (float32 [rows], or null): the shared part is multiplied by sigmoid(shared_gate[t]) before it is added.
 template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ place_of,
                                    const float* __restrict__ top_w, const T* __restrict__ shared_t,
                                    const float* __restrict__ shared_slices, int n_slices, long long slice_stride,
-                                   T* __restrict__ out, int H, int top) {
+                                   T* __restrict__ out, int H, int top, const float* __restrict__ shared_gate) {
   trigger_dependents();
   grid_dependency_wait();
   const int t = blockIdx.x;
+  const float sg = shared_gate != nullptr ? 1.f / (1.f + expf(-shared_gate[t])) : 1.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; k++) {
       const int p = place_of[(size_t)t * top + k];
       if (p >= 0) acc = fmaf(top_w[(size_t)t * top + k], to_float(y[(size_t)p * H + i]), acc);
     }
-    if (shared_t != nullptr) acc += to_float(shared_t[(size_t)t * H + i]);
-    for (int s = 0; s < n_slices; s++) acc += shared_slices[(size_t)s * slice_stride + (size_t)t * H + i];
+    if (shared_gate == nullptr) {
+      if (shared_t != nullptr) acc += to_float(shared_t[(size_t)t * H + i]);
+      for (int s = 0; s < n_slices; s++) acc += shared_slices[(size_t)s * slice_stride + (size_t)t * H + i];
+    } else {
+      float sh = shared_t != nullptr ? to_float(shared_t[(size_t)t * H + i]) : 0.f;
+      for (int s = 0; s < n_slices; s++) sh += shared_slices[(size_t)s * slice_stride + (size_t)t * H + i];
+      acc = fmaf(sg, sh, acc);
+    }
     out[(size_t)t * H + i] = from_float<T>(acc);
   }
 }
 
 template <typename T>
 int route_launch(const void* h, const float* wr, const float* br, const int* token_seq, int* top_idx, float* top_w,
-                 float* logits, int n_tokens, int H, int E, int top, cudaStream_t st) {
+                 float* logits, int n_tokens, int H, int E, int top, int over_all, float scale, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || (size_t)E * 4 * ROUTE_WARPS > 48 * 1024 || (E + 3) / 4 > 65535) return -2;
   const int tb = (n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
@@ -529,7 +553,7 @@ int route_launch(const void* h, const float* wr, const float* br, const int* tok
                       logits, n_tokens, H, E);
   if (rc != 0) return rc;
   return launch_pdl(moe_choose_kernel, dim3(tb), dim3(ROUTE_WARPS * 32), (size_t)ROUTE_WARPS * E * sizeof(float), st,
-                    (const float*)logits, token_seq, top_idx, top_w, n_tokens, E, top);
+                    (const float*)logits, token_seq, top_idx, top_w, n_tokens, E, top, over_all, scale);
 }
 
 template <typename T>
@@ -551,27 +575,27 @@ int route_scored_launch(const void* h, const float* wr, const float* br, const f
 
 template <typename TA, typename TC, int ACT>
 int gemm_launch(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets, const int* order, int top,
-                int n_places, int E, int N, int K, cudaStream_t st) {
+                int n_places, int E, int N, int K, cudaStream_t st, float limit = 0.f, float alpha = 0.f) {
   if (n_places <= 0 || N <= 0) return 0;
   if (K <= 0 || E <= 0) return -2;
   // few rows: every weight once, at full width (rows of 8 values must start on 16 bytes)
   const bool wide = K % 8 == 0 && lda % 8 == 0 && (((uintptr_t)A) & 15) == 0 && (((uintptr_t)W) & 15) == 0;
   if (wide && n_places <= GEMV_PLACES_MAX && E <= 65535)
     return launch_pdl(moe_gemv_kernel<TA, TC, ACT>, dim3((N + GV_FEATS - 1) / GV_FEATS, E), dim3(GV_WARPS * 32), 0, st,
-                      (const TA*)A, lda, (const TA*)W, (TC*)C, ldc, offsets, order, top, N, K);
+                      (const TA*)A, lda, (const TA*)W, (TC*)C, ldc, offsets, order, top, N, K, limit, alpha);
   const int row_tiles = n_places / BM + E;  // sum over experts of ceil(count / BM) is at most this
   if (row_tiles > 65535) return -3;
   return launch_pdl(moe_gemm_kernel<TA, TC, ACT>, dim3((N + BN - 1) / BN, row_tiles), dim3(256), 0, st, (const TA*)A,
-                    lda, (const TA*)W, (TC*)C, ldc, offsets, order, top, E, N, K);
+                    lda, (const TA*)W, (TC*)C, ldc, offsets, order, top, E, N, K, limit, alpha);
 }
 
 template <typename T, typename TY>
 int combine_launch(const void* y, const int* place_of, const float* top_w, const void* shared_t,
                    const float* shared_slices, int n_slices, long long slice_stride, void* out, int n_tokens, int H,
-                   int top, cudaStream_t st) {
+                   int top, const float* shared_gate, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   return launch_pdl(moe_combine_kernel<T, TY>, dim3(n_tokens), dim3(H >= 1024 ? 256 : 128), 0, st, (const TY*)y, place_of, top_w,
-                    (const T*)shared_t, shared_slices, n_slices, slice_stride, (T*)out, H, top);
+                    (const T*)shared_t, shared_slices, n_slices, slice_stride, (T*)out, H, top, shared_gate);
 }
 
 }  // namespace
@@ -587,12 +611,27 @@ TKB_EXPORT int tkb_moe_order(const int* top_idx, int n_pairs, int E, int top, in
 #define TKB_MOE_EXPORTS(SUF, T)                                                                                        \
   TKB_EXPORT int tkb_moe_route_##SUF(const void* h, const float* wr, const float* br, const int* token_seq,            \
                                      int* top_idx, float* top_w, float* logits, int n_tokens, int H, int E, int top,   \
-                                     void* st) {                                                                       \
-    return route_launch<T>(h, wr, br, token_seq, top_idx, top_w, logits, n_tokens, H, E, top, (cudaStream_t)st);       \
+                                     int over_all, float scale, void* st) {                                            \
+    return route_launch<T>(h, wr, br, token_seq, top_idx, top_w, logits, n_tokens, H, E, top, over_all, scale,         \
+                           (cudaStream_t)st);                                                                          \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_moe_logits_##SUF(const void* h, const float* wr, const float* br, float* logits, int n_tokens,    \
+                                      int H, int E, void* st) {                                                        \
+    if (n_tokens <= 0) return 0;                                                                                       \
+    if (E <= 0 || (E + 3) / 4 > 65535) return -2;                                                                      \
+    return launch_pdl(moe_logits_kernel<T>, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, (E + 3) / 4),             \
+                      dim3(ROUTE_WARPS * 32), 0, (cudaStream_t)st, (const T*)h, wr, br, logits, n_tokens, H, E);       \
   }                                                                                                                    \
   TKB_EXPORT int tkb_moe_gemm_gated_##SUF(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets, \
                                           const int* order, int top, int n_places, int E, int N, int K, void* st) {    \
     return gemm_launch<T, T, ACT_GATED>(A, lda, W, C, ldc, offsets, order, top, n_places, E, N, K, (cudaStream_t)st);  \
+  }                                                                                                                    \
+  TKB_EXPORT int tkb_moe_gemm_clamped_##SUF(const void* A, int lda, const void* W, void* C, int ldc,                   \
+                                            const int* offsets, const int* order, int top, int n_places, int E, int N, \
+                                            int K, float limit, float alpha, void* st) {                               \
+    if (!(limit > 0.f)) return -2;                                                                                     \
+    return gemm_launch<T, T, ACT_CLAMPED>(A, lda, W, C, ldc, offsets, order, top, n_places, E, N, K, (cudaStream_t)st, \
+                                          limit, alpha);                                                               \
   }                                                                                                                    \
   TKB_EXPORT int tkb_moe_gemm_gelu_##SUF(const void* A, int lda, const void* W, void* C, int ldc, const int* offsets,  \
                                          const int* order, int top, int n_places, int E, int N, int K, void* st) {     \
@@ -612,9 +651,9 @@ TKB_EXPORT int tkb_moe_order(const int* top_idx, int n_pairs, int E, int top, in
   }                                                                                                                    \
   TKB_EXPORT int tkb_moe_combine_##SUF(const float* y, const int* place_of, const float* top_w, const void* shared_t,  \
                                        const float* shared_slices, int n_slices, long long slice_stride, void* out,    \
-                                       int n_tokens, int H, int top, void* st) {                                       \
+                                       int n_tokens, int H, int top, const float* shared_gate, void* st) {             \
     return combine_launch<T, float>(y, place_of, top_w, shared_t, shared_slices, n_slices, slice_stride, out, n_tokens, \
-                                    H, top, (cudaStream_t)st);                                                         \
+                                    H, top, shared_gate, (cudaStream_t)st);                                            \
   }                                                                                                                    \
   TKB_EXPORT int tkb_moe_gather_##SUF(const void* src, const int* src_token, void* dst, int n_places, int H,           \
                                       void* st) {                                                                      \
@@ -629,15 +668,15 @@ TKB_MOE_EXPORTS(bf16, __nv_bfloat16)
 // The same weighted sum over expert outputs kept in bfloat16 (the tensor-core products' result).
 TKB_EXPORT int tkb_moe_combine_y16_bf16(const void* y, const int* place_of, const float* top_w, const void* shared_t,
                                         const float* shared_slices, int n_slices, long long slice_stride, void* out,
-                                        int n_tokens, int H, int top, void* st) {
+                                        int n_tokens, int H, int top, const float* shared_gate, void* st) {
   return combine_launch<__nv_bfloat16, __nv_bfloat16>(y, place_of, top_w, shared_t, shared_slices, n_slices, slice_stride,
-                                                      out, n_tokens, H, top, (cudaStream_t)st);
+                                                      out, n_tokens, H, top, shared_gate, (cudaStream_t)st);
 }
 
 // ... and its sum as float32 rows, for a consumer that reads float32 (a norm).
 TKB_EXPORT int tkb_moe_combine_y16_f32(const void* y, const int* place_of, const float* top_w, const void* shared_t,
                                        const float* shared_slices, int n_slices, long long slice_stride, void* out,
-                                       int n_tokens, int H, int top, void* st) {
+                                       int n_tokens, int H, int top, const float* shared_gate, void* st) {
   return combine_launch<float, __nv_bfloat16>(y, place_of, top_w, shared_t, shared_slices, n_slices, slice_stride, out,
-                                              n_tokens, H, top, (cudaStream_t)st);
+                                              n_tokens, H, top, shared_gate, (cudaStream_t)st);
 }

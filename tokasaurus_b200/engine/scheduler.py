@@ -140,7 +140,7 @@ class Scheduler:
         for g, group in enumerate(self.cache.groups):
             need = self.cache.pages_for(total - 1)
             if group.need.window:  # the least with which a token still sees its whole window
-                need = min(need, self.cache.pages_for(group.need.window + 1) + 1)
+                need = min(need, self.cache.pages_for(group.need.window + 1) + 1 + self.cache.kept_pages(g))
             if need > group.allocator.num_pages:
                 raise RequestTooLongError(
                     f"request {request.id!r} can need {need} pages of cache group {g}, its pool has "
@@ -179,8 +179,10 @@ class Scheduler:
 
     def _most_live(self, g: int) -> int:
         """Most pages a sequence holds at a time in the windowed group ``g``: the window, a step's tokens (and the
-        one token of a step launched ahead) and a page for where the window starts inside a page."""
-        return self.cache.pages_for(self.cache.groups[g].need.window + self.max_tokens + 1) + 1
+        one token of a step launched ahead) and a page for where the window starts inside a page, and the pages of the
+        first positions that the group's mixers keep in sight."""
+        return (self.cache.pages_for(self.cache.groups[g].need.window + self.max_tokens + 1) + 1
+                + self.cache.kept_pages(g))
 
     def _first_windowed_tokens(self, seq: Sequence) -> int:
         """How far windowed groups are filled at admission: the first step's tokens at most; the rest of a prompt

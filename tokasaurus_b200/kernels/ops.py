@@ -304,14 +304,16 @@ def rope_kv_write_partials(partials: torch.Tensor, q_out: torch.Tensor, position
            "rope_kv_write_partials")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> None:
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0, act: str = "silu") -> None:
     """out[t, i] = silu(gate[t, i]) * up[t, i].  interleave 0: gate_up = [gate | up]; interleave 8: columns in
-    groups of 16, 8 gate columns then the 8 up columns of the same features."""
+    groups of 16, 8 gate columns then the 8 up columns of the same features.  ``act`` "gelu_tanh": the tanh form of
+    GELU takes the SiLU's place."""
+    _need(act in ("silu", "gelu_tanh"), f"silu_mul: the gate's activation is 'silu' or 'gelu_tanh', not {act!r}")
     _need_cuda(gate_up, out)
     rows, two_i = gate_up.shape
     _need(two_i % 2 == 0 and out.shape == (rows, two_i // 2), "silu_mul: shapes")
     _need(gate_up.is_contiguous() and out.is_contiguous() and out.dtype == gate_up.dtype, "silu_mul: layout")
-    f = _fn(_libs.get("elementwise.cu"), f"tkb_silu_mul_{_suffix(out.dtype)}")
+    f = _fn(_libs.get("elementwise.cu"), f"tkb_{act}_mul_{_suffix(out.dtype)}")
     _check(f(_ptr(gate_up), _ptr(out), c_int(rows), c_int(two_i // 2), c_int(interleave), _stream()), "silu_mul")
 
 
@@ -834,11 +836,16 @@ def latent_prep(proj: torch.Tensor, q_off: int, q_rank: int, q_norm_w: torch.Ten
                 kv_off: int, rank: int, rot: int, rot_dims: int, kv_norm_w: torch.Tensor | None,
                 inv_freq: torch.Tensor | None, cache: torch.Tensor | None, positions: torch.Tensor,
                 token_seq: torch.Tensor, page_indptr: torch.Tensor, page_ids: torch.Tensor, page_size: int, eps: float,
-                status: torch.Tensor, act_dtype: torch.dtype) -> None:
+                status: torch.Tensor, act_dtype: torch.dtype, freq64: torch.Tensor | None = None, halves: bool = False,
+                mag: float = 1.0) -> None:
     """From float32 projections [T, .]: the RMS-normed query latent (columns q_off..+q_rank) into ``cq_out``; if
     ``kv_off`` >= 0 the RMS-normed latent (rank columns) and the rotated shared key part (rot columns, the first
-    ``rot_dims`` rotated in interleaved pairs) into the request's cache rows [pages, page_size, rank + rot]."""
-    _need_cuda(proj, q_norm_w, cq_out, kv_norm_w, inv_freq, cache, positions, token_seq, page_indptr, page_ids, status)
+    ``rot_dims`` rotated in interleaved pairs) into the request's cache rows [pages, page_size, rank + rot].
+    ``freq64`` float64 [rot_dims / 2] in place of ``inv_freq``: angles, sines and cosines in float64, times ``mag``;
+    ``halves``: channel i turns with channel i + rot_dims / 2."""
+    _need_cuda(proj, q_norm_w, cq_out, kv_norm_w, inv_freq, cache, positions, token_seq, page_indptr, page_ids, status, freq64)
+    _need(freq64 is None or (freq64.dtype == torch.float64 and freq64.is_contiguous() and freq64.numel() == rot_dims // 2),
+          "latent_prep: freq64 float64 [rot_dims / 2]")
     n = proj.shape[0]
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1, "latent_prep: float32 projections")
     if q_rank:
@@ -850,25 +857,30 @@ def latent_prep(proj: torch.Tensor, q_off: int, q_rank: int, q_norm_w: torch.Ten
         _need(cache is not None and cache.is_contiguous() and cache.dtype == act_dtype
               and tuple(cache.shape[1:]) == (1, page_size, rank + rot), "latent_prep: cache [pages, 1, page_size, rank + rot]")
         _need(kv_norm_w is not None and kv_norm_w.dtype == torch.float32 and kv_norm_w.numel() == rank, "latent_prep: norm weight")
-        _need(rot_dims == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2),
+        _need(rot_dims == 0 or freq64 is not None
+              or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2),
               "latent_prep: inv_freq float32 [rot_dims / 2]")
         num_pages = cache.shape[0]
     f = _fn(_libs.get("latent_attention.cu", TKB_LAT_RANK=rank), f"tkb_latent_prep_{_suffix(act_dtype)}")
     _check(f(_ptr(proj), c_int(proj.stride(0)), c_int(q_off), c_int(q_rank), _ptr(q_norm_w), _ptr(cq_out), c_int(kv_off),
              c_int(rot), c_int(rot_dims), _ptr(kv_norm_w), _ptr(inv_freq), _ptr(cache), _ptr(positions), _ptr(token_seq),
              _ptr(page_indptr), _ptr(page_ids), c_int(page_size), c_int(num_pages), c_float(eps), c_int(n), _ptr(status),
-             _stream()), "latent_prep")
+             _ptr(freq64), c_int(1 if halves else 0), c_float(mag), _stream()), "latent_prep")
 
 
 def rotate_pairs(x: torch.Tensor, n_heads: int, head_stride: int, off: int, rot: int, rot_dims: int,
                  inv_freq: torch.Tensor | None, positions: torch.Tensor, token_seq: torch.Tensor, rank: int,
-                 out: torch.Tensor | None = None, out_head_stride: int = 0, out_off: int = 0) -> None:
+                 out: torch.Tensor | None = None, out_head_stride: int = 0, out_off: int = 0,
+                 freq64: torch.Tensor | None = None, halves: bool = False, mag: float = 1.0) -> None:
     """Interleaved rotary encoding of the ``rot`` values at column ``off`` of every head of x [T, .]: the pairs
     (2i, 2i + 1), i < rot_dims / 2, are turned by position * inv_freq[i], the rest passes.  In place, or into the
-    columns ``out_off`` of every head of ``out`` [T, .]."""
-    _need_cuda(x, inv_freq, positions, token_seq, out)
+    columns ``out_off`` of every head of ``out`` [T, .].  ``freq64``, ``halves``, ``mag``: as in ``latent_prep``."""
+    _need_cuda(x, inv_freq, positions, token_seq, out, freq64)
+    _need(freq64 is None or (freq64.dtype == torch.float64 and freq64.is_contiguous() and freq64.numel() == rot_dims // 2),
+          "rotate_pairs: freq64 float64 [rot_dims / 2]")
     _need(x.stride(1) == 1 and off + rot <= head_stride and n_heads * head_stride <= x.shape[1], "rotate_pairs: layout")
-    _need(rot_dims == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2),
+    _need(rot_dims == 0 or freq64 is not None
+          or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2),
           "rotate_pairs: inv_freq float32 [rot_dims / 2]")
     if out is None:
         if rot_dims == 0:
@@ -879,7 +891,23 @@ def rotate_pairs(x: torch.Tensor, n_heads: int, head_stride: int, off: int, rot:
     f = _fn(_libs.get("latent_attention.cu", TKB_LAT_RANK=rank), f"tkb_rotate_pairs_{_suffix(x.dtype)}")
     _check(f(_ptr(x), c_int(x.stride(0)), c_int(head_stride), c_int(off), _ptr(out), c_int(out.stride(0)),
              c_int(out_head_stride), c_int(out_off), c_int(n_heads), c_int(rot), c_int(rot_dims), _ptr(inv_freq),
-             _ptr(positions), _ptr(token_seq), c_int(x.shape[0]), _stream()), "rotate_pairs")
+             _ptr(positions), _ptr(token_seq), c_int(x.shape[0]), _ptr(freq64), c_int(1 if halves else 0), c_float(mag),
+             _stream()), "rotate_pairs")
+
+
+def head_sigmoid_gate(val: torch.Tensor, gate: torch.Tensor, gate_off: int, rows: torch.Tensor | None, n_heads: int,
+                      vdim: int, rank: int) -> None:
+    """val [n_rows, heads * vdim] *= sigmoid(gate[token, gate_off + head]) in place: an output gate, one number a
+    (token, head).  ``gate`` float32 [T, .]; ``rows`` int32 names the tokens of val's rows (None: row r is token r).
+    ``rank``: the latent rank whose kernel module holds the kernel."""
+    _need_cuda(val, gate, rows)
+    _need(val.is_contiguous() and val.shape[1] == n_heads * vdim, "head_sigmoid_gate: val [rows, heads * vdim]")
+    _need(gate.dtype == torch.float32 and gate.stride(1) == 1 and gate_off + n_heads <= gate.shape[1],
+          "head_sigmoid_gate: float32 gate logits")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.numel() == val.shape[0]), "head_sigmoid_gate: rows")
+    f = _fn(_libs.get("latent_attention.cu", TKB_LAT_RANK=rank), f"tkb_head_sigmoid_gate_{_suffix(val.dtype)}")
+    _check(f(_ptr(val), _ptr(gate), c_int(gate.stride(0)), c_int(gate_off), _ptr(rows), c_int(val.shape[0]), c_int(n_heads),
+             c_int(vdim), _stream()), "head_sigmoid_gate")
 
 
 def latent_attn(q_abs: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, token_seq: torch.Tensor,
@@ -906,12 +934,15 @@ def latent_attn(q_abs: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, cac
 # ---------------------------------------------------------------------------------------------
 # Routed experts (csrc/moe.cu)
 def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: torch.Tensor | None, token_seq: torch.Tensor,
-              top: int, top_idx: torch.Tensor, top_w: torch.Tensor, scored: dict | None = None) -> None:
+              top: int, top_idx: torch.Tensor, top_w: torch.Tensor, scored: dict | None = None,
+              over_all: bool = False, scale: float = 1.0) -> None:
     """Router logits h @ router_w^T + router_b in float32, the ``top`` largest per token (int32 [T, top]) and the
     softmax over them (float32 [T, top]).  ``scored`` = dict(correction float32 [E] or None, groups, keep, scale): the
     other way of choosing: scores sigmoid(logits); the choice by score + correction among the experts of the best
     ``keep`` of ``groups`` equal groups of neighbours (a group scores the sum of its two largest choice scores); the
-    weights are the chosen scores over their sum, times ``scale``."""
+    weights are the chosen scores over their sum, times ``scale``.
+    ``over_all`` (the plain way of choosing): the weights are the chosen experts' shares of the softmax over ALL experts,
+    not renormalised; ``scale`` multiplies the plain way's weights."""
     _need_cuda(h, router_w, router_b, token_seq, top_idx, top_w)
     T, H = h.shape
     E = router_w.shape[0]
@@ -935,7 +966,20 @@ def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: torch.Tensor | 
         return
     f = _fn(_libs.get("moe.cu"), f"tkb_moe_route_{_suffix(h.dtype)}")
     _check(f(_ptr(h), _ptr(router_w), _ptr(router_b), _ptr(token_seq), _ptr(top_idx), _ptr(top_w), _ptr(logits), c_int(T),
-             c_int(H), c_int(E), c_int(top), _stream()), "moe_route")
+             c_int(H), c_int(E), c_int(top), c_int(1 if over_all else 0), c_float(scale), _stream()), "moe_route")
+
+
+def moe_logits(h: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None) -> None:
+    """out [T, E] = h @ w^T (+ bias) with float32 weights w [E, H], float32 sums: the router's first kernel alone, for
+    other small products that want float32 (a gate of one number a token)."""
+    _need_cuda(h, w, out, bias)
+    T, H = h.shape
+    E = w.shape[0]
+    _need(h.is_contiguous() and w.dtype == torch.float32 and w.is_contiguous() and w.shape[1] == H
+          and out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (T, E), "moe_logits: shapes")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "moe_logits: bias float32 [E]")
+    _check(_fn(_libs.get("moe.cu"), f"tkb_moe_logits_{_suffix(h.dtype)}")(
+        _ptr(h), _ptr(w), _ptr(bias), _ptr(out), c_int(T), c_int(H), c_int(E), _stream()), "moe_logits")
 
 
 def moe_order(top_idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, order: torch.Tensor,
@@ -973,11 +1017,13 @@ def moe_gather(src: torch.Tensor, src_token: torch.Tensor, out: torch.Tensor) ->
 
 
 def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, status: torch.Tensor,
-                         gated: bool = False, gelu: bool = False) -> torch.Tensor:
+                         gated: bool = False, gelu: bool = False, clamp: tuple[float, float] | None = None) -> torch.Tensor:
     """Row tile i (128 rows) of a[M, K] times the weights w[tile_group[i]] of w [groups, N, K], bfloat16 on the tcgen05
     tensor cores; tiles with tile_group[i] < 0 are left out (their rows of the result are not written).
     ``gated``: every group's rows interleave gate and up (``interleave_gate_up``); the result is [M, N / 2].
-    ``gelu`` (ungated): the exact GELU of every result in the epilogue."""
+    ``gelu`` (ungated): the exact GELU of every result in the epilogue.  ``clamp`` = (limit, alpha), with ``gated``:
+    the clamped unit g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), in the SiLU's
+    place."""
     _need_cuda(a, w, tile_group, status)
     G, N, K = w.shape
     _need(can_use_tcgen05(a, w.view(G * N, K)) and a.shape[1] == K, "gemm_tcgen05_grouped: bfloat16, K a multiple of 8")
@@ -986,6 +1032,12 @@ def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Ten
     _need(not gated or N % 16 == 0, "gemm_tcgen05_grouped: gated rows come in groups of 16")
     _need(not (gated and gelu), "gemm_tcgen05_grouped: the GELU epilogue is the ungated form's")
     out = torch.empty((M, N // 2 if gated else N), dtype=torch.bfloat16, device=a.device)
+    if clamp is not None:
+        _need(gated and clamp[0] > 0, "gemm_tcgen05_grouped: the clamped unit is a gated form with a positive limit")
+        _check(_fn(_libs.get("gemm_tcgen05.cu"), "tkb_gemm_tcgen05_grouped_clamped_bf16")(
+            _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(K), _ptr(out), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
+            c_float(clamp[0]), c_float(clamp[1]), _ptr(tile_group), c_int(G), _ptr(status), _stream()), "gemm_tcgen05_grouped")
+        return out
     _check(_fn(_libs.get("gemm_tcgen05.cu"), "tkb_gemm_tcgen05_grouped_bf16")(
         _ptr(a), c_int(a.stride(0)), _ptr(w), c_int(K), _ptr(out), c_int(out.stride(0)), c_int(M), c_int(N), c_int(K),
         c_int(1 if gated else (2 if gelu else 0)), _ptr(tile_group), c_int(G), _ptr(status), _stream()), "gemm_tcgen05_grouped")
@@ -993,17 +1045,24 @@ def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Ten
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor | None,
-             top: int, gated: bool, gelu: bool = False) -> None:
+             top: int, gated: bool, gelu: bool = False, clamp: tuple[float, float] | None = None) -> None:
     """The experts' products over the ordering.  w [E, N (2N if gated), K]; a [., K]; row p of ``out`` is made from
     row order[p] // top of ``a`` (row p if ``order`` is None) with the weights of the expert whose span holds p.
     gated: out = silu(a w_gate^T) * (a w_up^T) in a's type [places, N]; gelu: out = gelu(a w^T) (exact) in a's type;
-    else float32 [places, N]."""
+    else float32 [places, N].  ``clamp`` = (limit, alpha), with ``gated``: the clamped unit
+    g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), in the SiLU's place."""
     _need_cuda(a, w, out, offsets, order)
+    _need(clamp is None or (gated and clamp[0] > 0), "moe_gemm: the clamped unit is a gated form with a positive limit")
     E, NN, K = w.shape
     N = NN // 2 if gated else NN
     _need(a.dtype == w.dtype and a.stride(1) == 1 and a.shape[1] == K and w.is_contiguous(), "moe_gemm: operands")
     _need(not (gated and gelu), "moe_gemm: gated or gelu")
     _need(out.shape[1] == N and out.stride(1) == 1 and out.dtype == (a.dtype if (gated or gelu) else torch.float32), "moe_gemm: out")
+    if clamp is not None:
+        _check(_fn(_libs.get("moe.cu"), f"tkb_moe_gemm_clamped_{_suffix(a.dtype)}")(
+            _ptr(a), c_int(a.stride(0)), _ptr(w), _ptr(out), c_int(out.stride(0)), _ptr(offsets), _ptr(order), c_int(top),
+            c_int(out.shape[0]), c_int(E), c_int(N), c_int(K), c_float(clamp[0]), c_float(clamp[1]), _stream()), "moe_gemm")
+        return
     name = f"tkb_moe_gemm_{'gated_' if gated else ('gelu_' if gelu else '')}{_suffix(a.dtype)}"
     _check(_fn(_libs.get("moe.cu"), name)(_ptr(a), c_int(a.stride(0)), _ptr(w), _ptr(out), c_int(out.stride(0)),
                                           _ptr(offsets), _ptr(order), c_int(top), c_int(out.shape[0]), c_int(E), c_int(N),
@@ -1011,10 +1070,13 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch
 
 
 def moe_combine(y: torch.Tensor, place_of: torch.Tensor, top_w: torch.Tensor, shared: torch.Tensor | None,
-                out: torch.Tensor) -> None:
+                out: torch.Tensor, shared_gate: torch.Tensor | None = None) -> None:
     """out[t] = sum_k top_w[t, k] * y[place_of[t, k]] (+ shared[t]); y float32 [places, H]; shared [T, H] in out's type
-    or float32 slices [slices, T, H]."""
-    _need_cuda(y, place_of, top_w, shared, out)
+    or float32 slices [slices, T, H].  ``shared_gate`` float32 [T]: the shared part counts sigmoid(shared_gate[t])
+    times."""
+    _need_cuda(y, place_of, top_w, shared, out, shared_gate)
+    _need(shared_gate is None or (shared is not None and shared_gate.dtype == torch.float32 and shared_gate.is_contiguous()
+                                  and shared_gate.numel() == out.shape[0]), "moe_combine: shared gate float32 [T]")
     T, H = out.shape
     top = top_w.shape[1]
     _need(y.is_contiguous() and y.shape[1] == H and out.is_contiguous(), "moe_combine: y, out")
@@ -1023,7 +1085,7 @@ def moe_combine(y: torch.Tensor, place_of: torch.Tensor, top_w: torch.Tensor, sh
     f = _fn(_libs.get("moe.cu"), f"tkb_moe_combine_y16_{_suffix(out.dtype)}" if y.dtype == torch.bfloat16
             else f"tkb_moe_combine_{_suffix(out.dtype)}")
     _check(f(_ptr(y), _ptr(place_of), _ptr(top_w), _ptr(d), _ptr(sl), c_int(n_sl), ctypes.c_longlong(stride), _ptr(out),
-             c_int(T), c_int(H), c_int(top), _stream()), "moe_combine")
+             c_int(T), c_int(H), c_int(top), _ptr(shared_gate), _stream()), "moe_combine")
 
 
 # ---------------------------------------------------------------------------------------------
@@ -1310,10 +1372,17 @@ def silu_cols(x: torch.Tensor, ncols: int, defines: dict) -> None:
 
 # ---------------------------------------------------------------------------------------------
 # Attention with a score cap and a sink, keys and values of different sizes (csrc/attention_sink.cu)
-def sink_attention_defines(dim: int, vdim: int, sigmoid: bool = False) -> dict:
-    """``sigmoid``: the build whose weights are sigmoid(score), not a softmax."""
+def sink_attention_defines(dim: int, vdim: int, sigmoid: bool = False, maps: int = 1) -> dict:
+    """``sigmoid``: the build whose weights are sigmoid(score), not a softmax.  ``maps``: attention maps a head (each
+    with query and key vectors of its own, over the same values)."""
     _need(0 < dim <= 512 and 0 < vdim <= 512, f"sink attention: head sizes up to 512, not {dim} / {vdim}")
-    return dict(TKB_QK=dim, TKB_VD=vdim, TKB_SIGMOID=1) if sigmoid else dict(TKB_QK=dim, TKB_VD=vdim)
+    _need(1 <= maps <= 4, f"sink attention: one to four maps a head, not {maps}")
+    d = dict(TKB_QK=dim, TKB_VD=vdim)
+    if sigmoid:
+        d["TKB_SIGMOID"] = 1
+    if maps > 1:
+        d["TKB_MAPS"] = maps
+    return d
 
 
 def sink_attn_prep(qkv: torch.Tensor, bias: torch.Tensor | None, unit_norm: bool, eps: float, q_out: torch.Tensor,
@@ -1321,27 +1390,28 @@ def sink_attn_prep(qkv: torch.Tensor, bias: torch.Tensor | None, unit_norm: bool
                    page_ids: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int,
                    write_cache: bool, status: torch.Tensor, norm_w: torch.Tensor | None = None,
                    rot_freq: torch.Tensor | None = None, rot_dims: int = 0, rot_pairs: bool = False,
-                   values_are_keys: bool = False, sigmoid: bool = False) -> None:
-    """qkv float32 [T, heads*dim | kv heads*dim | kv heads*vdim] -> (+ bias, q and k heads divided by their root mean
-    square) q_out [T, heads*dim] and the tokens' [k | v] rows in cache [pages, kv heads, page_size, dim + vdim].
+                   values_are_keys: bool = False, sigmoid: bool = False, maps: int = 1) -> None:
+    """qkv float32 [T, heads*maps*dim | kv heads*maps*dim | kv heads*vdim | anything else] -> (+ bias, q and k vectors
+    divided by their root mean square) q_out [T, heads*maps*dim] and the tokens' [k of every map | v] rows in cache
+    [pages, kv heads, page_size, maps*dim + vdim].
     ``norm_w`` float32 [2, dim]: weights of the q heads' and the k heads' norm.  ``rot_freq`` float64 [rot_dims / 2]:
     q and k are rotated by position on their first ``rot_dims`` channels (``rot_pairs``: channel 2i with 2i + 1, else
     i with i + rot_dims / 2).  ``values_are_keys``: the projections hold no v; a token's value is its key as projected
     (before norm and rotation).  ``sigmoid``: the kernel build of the sigmoid form."""
     _need_cuda(qkv, bias, q_out, cache, positions, token_seq, page_indptr, page_ids, status, norm_w, rot_freq)
     T = qkv.shape[0]
-    C = (n_heads + n_kv_heads) * dim + (0 if values_are_keys else n_kv_heads * vdim)
-    _need(not values_are_keys or dim == vdim, "sink_attn_prep: values that are the keys have the keys' size")
+    C = (n_heads + n_kv_heads) * maps * dim + (0 if values_are_keys else n_kv_heads * vdim)
+    _need(not values_are_keys or (dim == vdim and maps == 1), "sink_attn_prep: values that are the keys have the keys' size")
     _need(norm_w is None or (norm_w.dtype == torch.float32 and norm_w.is_contiguous() and tuple(norm_w.shape) == (2, dim)),
           "sink_attn_prep: norm weights float32 [2, dim]")
     _need(rot_freq is None or (rot_freq.dtype == torch.float64 and rot_freq.is_contiguous() and rot_dims % 2 == 0
                                and 0 < rot_dims <= dim and rot_freq.numel() == rot_dims // 2),
           "sink_attn_prep: float64 [rot_dims / 2] frequencies")
-    _need(qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] == C, "sink_attn_prep: float32 projections")
+    _need(qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] >= C, "sink_attn_prep: float32 projections")
     _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C), "sink_attn_prep: bias float32")
-    _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, n_heads * dim) and q_out.dtype == cache.dtype, "sink_attn_prep: q_out")
-    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, dim + vdim), "sink_attn_prep: cache rows")
-    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, sigmoid)), f"tkb_sink_attn_prep_{_suffix(cache.dtype)}")(
+    _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, n_heads * maps * dim) and q_out.dtype == cache.dtype, "sink_attn_prep: q_out")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, maps * dim + vdim), "sink_attn_prep: cache rows")
+    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, sigmoid, maps)), f"tkb_sink_attn_prep_{_suffix(cache.dtype)}")(
         _ptr(qkv), c_int(qkv.stride(0)), _ptr(bias), c_int(1 if unit_norm else 0), c_float(eps), _ptr(q_out), _ptr(cache),
         _ptr(positions), _ptr(token_seq), _ptr(page_indptr), _ptr(page_ids), c_int(T), c_int(n_heads), c_int(n_kv_heads),
         c_int(page_size), c_int(cache.shape[0]), c_int(1 if write_cache else 0), _ptr(status), _ptr(norm_w), _ptr(rot_freq),
@@ -1354,26 +1424,36 @@ def _head_vectors(n_heads: int, what: str, *vectors):
         _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == n_heads), f"{what}: float32 [heads] vectors")
 
 
+def _sink_out_ok(out: torch.Tensor, rows: int, n_heads: int, vdim: int, maps: int, act: torch.dtype) -> bool:
+    """One map: [rows, heads * vdim] in the activation type.  Several: float32 [rows, heads * maps * vdim], the maps'
+    outputs side by side, unrounded."""
+    return (out.is_contiguous() and tuple(out.shape) == (rows, n_heads * maps * vdim)
+            and out.dtype == (act if maps == 1 else torch.float32))
+
+
 def attn_sink(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
               page_indptr: torch.Tensor, page_ids: torch.Tensor, rows: torch.Tensor | None, n_rows: int,
               sinks: torch.Tensor | None, n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int,
               scale: float, softcap: float | None, window: int | None, status: torch.Tensor,
-              head_scale: torch.Tensor | None = None, head_bias: torch.Tensor | None = None, sigmoid: bool = False) -> None:
+              head_scale: torch.Tensor | None = None, head_bias: torch.Tensor | None = None, sigmoid: bool = False,
+              maps: int = 1, keep_first: int = 0) -> None:
     """Attention of ``n_rows`` tokens (``rows`` names them; None: all) over their requests' cached [k | v] rows.
     ``head_scale`` / ``head_bias`` float32 [heads]: a factor on a head's scale, a number added to its scores.
-    ``sigmoid``: weights sigmoid(score) instead of a softmax (no sink)."""
+    ``sigmoid``: weights sigmoid(score) instead of a softmax (no sink).  ``maps`` > 1: so many attention maps a head,
+    each a softmax of its own; ``out`` then is float32 [rows, heads * maps * vdim].  ``keep_first``: with a window, the
+    request's first so many positions stay visible."""
     _need_cuda(q, out, cache, token_seq, positions, page_indptr, page_ids, rows, sinks, status, head_scale, head_bias)
-    _head_vectors(n_heads, "attn_sink", head_scale, head_bias)
+    _head_vectors(n_heads * maps, "attn_sink", head_scale, head_bias)
     _need(not (sigmoid and sinks is not None), "attn_sink: the sigmoid form has no sink")
-    _need(q.is_contiguous() and q.shape[1] == n_heads * dim and q.dtype == cache.dtype and out.dtype == cache.dtype
-          and out.is_contiguous() and tuple(out.shape) == (n_rows, n_heads * vdim), "attn_sink: q and out")
-    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, dim + vdim), "attn_sink: cache rows")
-    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads), "attn_sink: sinks float32 [heads]")
-    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, sigmoid)), f"tkb_attn_sink_simt_{_suffix(cache.dtype)}")(
+    _need(q.is_contiguous() and q.shape[1] == n_heads * maps * dim and q.dtype == cache.dtype
+          and _sink_out_ok(out, n_rows, n_heads, vdim, maps, cache.dtype), "attn_sink: q and out")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, maps * dim + vdim), "attn_sink: cache rows")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads * maps), "attn_sink: sinks float32 [heads]")
+    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, sigmoid, maps)), f"tkb_attn_sink_simt_{_suffix(cache.dtype)}")(
         _ptr(q), _ptr(out), _ptr(cache), _ptr(token_seq), _ptr(positions), _ptr(page_indptr), _ptr(page_ids), _ptr(rows),
         c_int(n_rows), _ptr(sinks), c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale),
-        c_float(softcap or 0.0), c_int(window or 0), c_int(cache.shape[0]), _ptr(status), _ptr(head_scale), _ptr(head_bias),
-        _stream()), "attn_sink")
+        c_float(softcap or 0.0), c_int(window or 0), c_int(keep_first if window else 0), c_int(cache.shape[0]),
+        _ptr(status), _ptr(head_scale), _ptr(head_bias), _stream()), "attn_sink")
 
 
 def can_use_attn_sink_tc(dtype: torch.dtype, dim: int, vdim: int) -> bool:
@@ -1387,36 +1467,56 @@ def attn_sink_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, seq_q_
                  sinks: torch.Tensor | None, n_heads: int, n_kv_heads: int, dim: int, vdim: int, page_size: int, scale: float,
                  softcap: float | None, window: int | None, status: torch.Tensor, portions: bool = True,
                  singles: bool = True, head_scale: torch.Tensor | None = None, head_bias: torch.Tensor | None = None,
-                 sigmoid: bool = False) -> None:
-    """Attention of every token of the step on the tensor cores (bfloat16): out [T, heads * vdim].  ``portions`` /
-    ``singles``: whether the step can hold requests with several tokens / with one (a kernel each)."""
+                 sigmoid: bool = False, maps: int = 1, keep_first: int = 0) -> None:
+    """Attention of every token of the step on the tensor cores (bfloat16): out [T, heads * vdim] (``maps`` > 1: float32
+    [T, heads * maps * vdim]).  ``portions`` / ``singles``: whether the step can hold requests with several tokens /
+    with one (a kernel each).  ``keep_first``: as in ``attn_sink``."""
     _need_cuda(q, out, cache, seq_q_start, seq_q_len, seq_kv_len, page_indptr, page_ids, sinks, status, head_scale, head_bias)
-    _head_vectors(n_heads, "attn_sink_tc", head_scale, head_bias)
+    _head_vectors(n_heads * maps, "attn_sink_tc", head_scale, head_bias)
     _need(not (sigmoid and sinks is not None), "attn_sink_tc: the sigmoid form has no sink")
     T = q.shape[0]
     _need(can_use_attn_sink_tc(cache.dtype, dim, vdim), "attn_sink_tc: bfloat16 rows, key and value sizes multiples of 16")
-    _need(q.is_contiguous() and q.shape[1] == n_heads * dim and q.dtype == cache.dtype and out.dtype == cache.dtype
-          and out.is_contiguous() and tuple(out.shape) == (T, n_heads * vdim), "attn_sink_tc: q and out")
-    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, dim + vdim), "attn_sink_tc: cache rows")
-    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads), "attn_sink_tc: sinks float32 [heads]")
+    _need(q.is_contiguous() and q.shape[1] == n_heads * maps * dim and q.dtype == cache.dtype
+          and _sink_out_ok(out, T, n_heads, vdim, maps, cache.dtype), "attn_sink_tc: q and out")
+    _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, maps * dim + vdim), "attn_sink_tc: cache rows")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == n_heads * maps), "attn_sink_tc: sinks float32 [heads]")
     # single tokens: with few requests a request's 64-key tiles are shared out among blocks until the SMs are covered
     # twice (a function of the step's shape only: the same step replays from a graph)
     splits, part = 1, None
     if singles:
         from tokasaurus_b200.kernels.device import device_limits
 
-        blocks = n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
+        blocks = n_seqs * n_kv_heads * maps * ((n_heads // n_kv_heads + 15) // 16)
         splits = max(1, min(8, (2 * device_limits(q.device).sm_count) // max(1, blocks)))
         if window:
             splits = min(splits, max(1, (window + 63) // 64))
         if splits > 1:
-            part = torch.empty((n_seqs * n_heads * splits * (vdim + 2),), dtype=torch.float32, device=q.device)
-    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, sigmoid)), "tkb_attn_sink_tc_bf16")(
+            part = torch.empty((n_seqs * n_heads * maps * splits * (vdim + 2),), dtype=torch.float32, device=q.device)
+    _check(_fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, sigmoid, maps)), "tkb_attn_sink_tc_bf16")(
         _ptr(q), _ptr(out), _ptr(cache), _ptr(seq_q_start), _ptr(seq_q_len), _ptr(seq_kv_len), _ptr(page_indptr),
         _ptr(page_ids), c_int(T), c_int(n_seqs), c_int(1 if portions else 0), c_int(1 if singles else 0), _ptr(sinks),
         c_int(n_heads), c_int(n_kv_heads), c_int(page_size), c_float(scale), c_float(softcap or 0.0), c_int(window or 0),
-        c_int(cache.shape[0]), _ptr(status), _ptr(part), c_int(splits), _ptr(head_scale), _ptr(head_bias), _stream()),
-        "attn_sink_tc")
+        c_int(keep_first if window else 0), c_int(cache.shape[0]), _ptr(status), _ptr(part), c_int(splits), _ptr(head_scale),
+        _ptr(head_bias), _stream()), "attn_sink_tc")
+
+
+def diff_combine(a: torch.Tensor, lam: torch.Tensor, eps: float, mult: float, gate: torch.Tensor | None, gate_off: int,
+                 rows: torch.Tensor | None, out: torch.Tensor, n_heads: int, dim: int, vdim: int) -> None:
+    """The differential form's combination of two attention maps: a float32 [n_rows, heads * 2 * vdim] ->
+    out [n_rows, heads * vdim] = N(a_0 - lam * a_1) * mult * sigmoid(gate[token, gate_off + head]), N the division of a
+    head's vdim values by their root mean square (float32, ``eps``).  ``lam`` float32 [1] on the device; ``gate``
+    float32 [T, .] or None; ``rows`` int32 names the tokens of a's rows (None: row r is token r)."""
+    _need_cuda(a, lam, gate, rows, out)
+    n_rows = a.shape[0]
+    _need(a.dtype == torch.float32 and a.is_contiguous() and a.shape[1] == n_heads * 2 * vdim
+          and out.is_contiguous() and tuple(out.shape) == (n_rows, n_heads * vdim), "diff_combine: a and out")
+    _need(lam.dtype == torch.float32 and lam.numel() == 1, "diff_combine: lambda float32 [1]")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate_off + n_heads <= gate.shape[1]),
+          "diff_combine: float32 gate logits")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.numel() == n_rows), "diff_combine: rows")
+    f = _fn(_libs.get("attention_sink.cu", **sink_attention_defines(dim, vdim, False, 2)), f"tkb_diff_combine_{_suffix(out.dtype)}")
+    _check(f(_ptr(a), _ptr(lam), c_float(eps), c_float(mult), _ptr(gate), c_int(gate.stride(0) if gate is not None else 0),
+             c_int(gate_off), _ptr(rows), _ptr(out), c_int(n_rows), c_int(n_heads), _stream()), "diff_combine")
 
 
 def prepare_modules(modules) -> None:

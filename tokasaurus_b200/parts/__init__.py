@@ -24,6 +24,7 @@ from tokasaurus_b200.parts.recurrent import (  # noqa: F401
 )
 from tokasaurus_b200.parts.state_space import SelectiveStateSpace  # noqa: F401
 from tokasaurus_b200.parts.sink_attention import SinkAttention  # noqa: F401
+from tokasaurus_b200.parts.diff_attention import DifferentialAttention  # noqa: F401
 from tokasaurus_b200.parts.latent_attention import LatentAttention  # noqa: F401
 from tokasaurus_b200.parts.side_input import TokenSideInput  # noqa: F401
 from tokasaurus_b200.parts.block import OutputNormBlock, PostNormBlock, PreNormBlock  # noqa: F401

@@ -46,12 +46,14 @@ class WeightSpec:
 class PagedCacheNeed:
     """Per-token keys and values kept in pages.  ``window``: only the last ``window`` keys
     (the query's own included) are ever read, so pages behind it can be given back.  ``planes``: 2 for keys and
-    values, 1 for a mixer that keeps one row a token (a latent from which it makes both)."""
+    values, 1 for a mixer that keeps one row a token (a latent from which it makes both).  ``keep_first``: with a
+    window, the request's first so many keys are read by every later query too: their pages stay."""
 
     n_kv_heads: int
     head_dim: int
     window: int | None = None
     planes: int = 2
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

@@ -11,7 +11,15 @@ from tokasaurus_b200.parts.base import FeedForward, WeightSpec
 
 
 class GatedMLP(FeedForward):
-    def __init__(self, width: int, inner: int, gate_name: str, up_name: str, down_name: str):
+    """``activation`` "gelu_tanh": the gate goes through the tanh form of GELU instead of the SiLU (the products whose
+    epilogue is the SiLU gate are then not used).  ``out_f32``: the update leaves as float32 rows or as the float32
+    slices of a K-split product, for the residual sum."""
+
+    def __init__(self, width: int, inner: int, gate_name: str, up_name: str, down_name: str, activation: str = "silu",
+                 out_f32: bool = False):
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"the gate's activation is 'silu' or 'gelu_tanh', not {activation!r}")
+        self.activation, self.out_f32 = activation, bool(out_f32)
         self.width = width
         self.inner = inner
         self.names = (gate_name, up_name, down_name)
@@ -42,6 +50,11 @@ class GatedMLP(FeedForward):
         """Returns the update [rows, width] in h's dtype, or as float32 slices [slices, rows, width]
         that the next norm adds (few rows, bfloat16)."""
         status = ctx.status if ctx is not None else None
+        if self.activation != "silu":
+            gu = ops.linear(h, self.w_gate_up)
+            act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
+            ops.silu_mul(gu, act, self.interleave, act=self.activation)
+            return ops.linear_out_f32(act, self.w_down, status) if self.out_f32 else ops.linear(act, self.w_down)
         if self.interleave and ops.can_use_few_rows(h, self.w_gate_up) and self.w_gate_up.shape[0] % 16 == 0:
             act = ops.linear_few_rows_gated(h, self.w_gate_up, status)
             return ops.linear_few_rows(act, self.w_down, status)
@@ -142,7 +155,13 @@ class RoutedExperts(FeedForward):
     the experts of the best ``keep`` of ``groups`` equal groups of neighbours only (a group scores the sum of its two
     largest choice scores); the weights are the chosen experts' s over their sum, times ``scale``.
     ``expert="gelu"``: an expert is ``down(gelu(up h))`` with the exact GELU and no gate; ``expert_names(e)`` then gives
-    (up, down).  ``out_dtype`` float32: the weighted sum leaves as float32 rows (for a norm that reads it)."""
+    (up, down).  ``out_dtype`` float32: the weighted sum leaves as float32 rows (for a norm that reads it).
+
+    ``over_all`` = dict(scale): a third way of weighing: the choice is the plain one (largest logits), the weights are
+    the chosen experts' shares of the softmax over ALL experts, times ``scale``, not renormalised.
+    ``expert="clamped"`` with ``clamp`` = (limit, alpha): an expert is ``down(g * sigmoid(alpha g) * (u + 1))`` with
+    g = min(gate(h), limit), u = clamp(up(h), -limit, limit).  ``shared_gate_name``: a vector [1, width]; the shared
+    expert's output counts sigmoid(that vector . h) times, one number a token (float32)."""
 
     # (token, choice) pairs from which the gathered tcgen05 products are used (bfloat16).  Below, the few-rows kernel
     # fetches every chosen expert's weights once as well, but spends one multiply-add a row on every weight it
@@ -153,12 +172,22 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, width: int, inner: int, n_experts: int, top: int, router_name: str, router_bias_name: str | None,
                  expert_names, shared: FeedForward | None = None, scored: dict | None = None, expert: str = "silu_gated",
-                 out_dtype: torch.dtype | None = None):
+                 out_dtype: torch.dtype | None = None, over_all: dict | None = None, clamp: tuple[float, float] | None = None,
+                 shared_gate_name: str | None = None):
         """``expert_names(e)`` -> (gate, up, down) tensor names of expert e."""
         if not 0 < top <= n_experts:
             raise ValueError(f"top={top} of {n_experts} experts")
-        if expert not in ("silu_gated", "gelu"):
-            raise ValueError(f"an expert is 'silu_gated' or 'gelu', not {expert!r}")
+        if expert not in ("silu_gated", "gelu", "clamped"):
+            raise ValueError(f"an expert is 'silu_gated', 'gelu' or 'clamped', not {expert!r}")
+        if (expert == "clamped") != (clamp is not None) or (clamp is not None and not clamp[0] > 0):
+            raise ValueError("a clamped expert has a positive limit and a factor, other experts neither")
+        if over_all is not None and scored is not None:
+            raise ValueError("the weights come from the softmax over all experts or from sigmoid scores, not both")
+        if shared_gate_name is not None and shared is None:
+            raise ValueError("a gate on the shared expert needs a shared expert")
+        self.over_all = over_all
+        self.clamp = (float(clamp[0]), float(clamp[1])) if clamp is not None else None
+        self.shared_gate_name = shared_gate_name
         if scored is not None:
             g, keep = int(scored.get("groups", 1)), int(scored.get("keep", 1))
             if g <= 0 or n_experts % g or not 0 < keep <= g or top > keep * (n_experts // g):
@@ -179,6 +208,8 @@ class RoutedExperts(FeedForward):
             specs += [WeightSpec(n, (self.inner, self.width)) for n in names[:-1]] + [WeightSpec(names[-1], (self.width, self.inner))]
         if self.shared is not None:
             specs += list(self.shared.weight_specs())
+        if self.shared_gate_name is not None:
+            specs.append(WeightSpec(self.shared_gate_name, (1, self.width), role="vector"))
         return tuple(specs)
 
     def kernel_modules(self, dtype):
@@ -187,6 +218,9 @@ class RoutedExperts(FeedForward):
 
     def bind(self, weights, rt) -> None:
         self.router_w = weights[self.router_name].contiguous()
+        # the shared expert's gate: a one-row product in float32, like the router's own
+        self.shared_gate_w = (weights[self.shared_gate_name].float().view(1, self.width).contiguous()
+                              if self.shared_gate_name is not None else None)
         self.router_b = weights[self.router_bias_name].contiguous() if self.router_bias_name is not None else None
         self.route_args = None
         if self.scored is not None:
@@ -215,7 +249,12 @@ class RoutedExperts(FeedForward):
         top_w = torch.empty((T, top), dtype=torch.float32, device=dev)
         # rows of padding tokens (a step graph's) choose nothing; a cut-down set of rows has none
         token_seq = ctx.token_seq if (ctx is not None and T == ctx.n_tokens) else None
-        ops.moe_route(h, self.router_w, self.router_b, token_seq, top, top_idx, top_w, self.route_args)
+        ops.moe_route(h, self.router_w, self.router_b, token_seq, top, top_idx, top_w, self.route_args,
+                      over_all=self.over_all is not None, scale=float((self.over_all or {}).get("scale", 1.0)))
+        shared_gate = None
+        if self.shared_gate_name is not None:
+            shared_gate = torch.empty((T,), dtype=torch.float32, device=dev)
+            ops.moe_logits(h, self.shared_gate_w, shared_gate.view(T, 1))
         offsets = torch.empty((E + 1,), dtype=torch.int32, device=dev)
         place_of = torch.empty((T * top,), dtype=torch.int32, device=dev)
         shared = self.shared.forward(ctx, h) if self.shared is not None else None
@@ -232,15 +271,16 @@ class RoutedExperts(FeedForward):
             rows = torch.empty((n_tiles * tile, self.width), dtype=h.dtype, device=dev)
             ops.moe_gather(h, src_token, rows)
             status = ctx.status if ctx is not None else torch.zeros(1, dtype=torch.int32, device=dev)
-            act = ops.gemm_tcgen05_grouped(rows, self.w_gate_up_tc, tile_group, status, gated=not self.gelu, gelu=self.gelu)
+            act = ops.gemm_tcgen05_grouped(rows, self.w_gate_up_tc, tile_group, status, gated=not self.gelu, gelu=self.gelu,
+                                           clamp=self.clamp)
             y = ops.gemm_tcgen05_grouped(act, self.w_down, tile_group, status)
-            ops.moe_combine(y, place_of, top_w, shared, out)
+            ops.moe_combine(y, place_of, top_w, shared, out, shared_gate)
             return out
         order = torch.empty((T * top,), dtype=torch.int32, device=dev)
         ops.moe_order(top_idx, E, offsets, order, place_of)
         act = torch.empty((T * top, self.inner), dtype=h.dtype, device=dev)
-        ops.moe_gemm(h, self.w_gate_up, act, offsets, order, top, gated=not self.gelu, gelu=self.gelu)
+        ops.moe_gemm(h, self.w_gate_up, act, offsets, order, top, gated=not self.gelu, gelu=self.gelu, clamp=self.clamp)
         y = torch.empty((T * top, self.width), dtype=torch.float32, device=dev)
         ops.moe_gemm(act, self.w_down, y, offsets, None, top, gated=False)
-        ops.moe_combine(y, place_of, top_w, shared, out)
+        ops.moe_combine(y, place_of, top_w, shared, out, shared_gate)
         return out

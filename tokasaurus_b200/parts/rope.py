@@ -13,6 +13,10 @@ kernel, in float32, as the same product.
              wavelen < orig/high_freq_factor  ->  inv_freq
              otherwise  smooth = (orig/wavelen - low) / (high - low);
                         (1 - smooth) * inv_freq / factor + smooth * inv_freq
+    yarn:    turns(t) = rotary_dim * ln(orig / (2 pi t)) / (2 ln theta)      (the pair index that makes t turns in orig positions)
+             lo = max(floor(turns(fast)), 0),  hi = min(ceil(turns(slow)), rotary_dim - 1)
+             ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1)
+             inv_freq_j / factor * ramp_j + inv_freq_j * (1 - ramp_j);   cos and sin times 0.1 ln(factor) + 1
 """
 
 from __future__ import annotations
@@ -37,10 +41,10 @@ class RotaryEncoding(PositionEncoding):
 
     def __init__(self, rotary_dim: int, theta: float, scaling_type: str = "default", factor: float = 1.0,
                  low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
-                 original_max_position_embeddings: int = 8192):
+                 original_max_position_embeddings: int = 8192, yarn_fast: float = 32.0, yarn_slow: float = 1.0):
         if rotary_dim <= 0 or rotary_dim % 2:
             raise ValueError(f"rotary_dim must be a positive even number, got {rotary_dim}")
-        if scaling_type not in ("default", "llama3"):
+        if scaling_type not in ("default", "llama3", "yarn"):
             raise ValueError(f"unknown rotary scaling {scaling_type!r}")
         self.rotary_dim = rotary_dim
         self.theta = float(theta)
@@ -49,18 +53,38 @@ class RotaryEncoding(PositionEncoding):
         self.low_freq_factor = float(low_freq_factor)
         self.high_freq_factor = float(high_freq_factor)
         self.original_max_position_embeddings = int(original_max_position_embeddings)
+        self.yarn_fast, self.yarn_slow = float(yarn_fast), float(yarn_slow)
+        if scaling_type == "yarn" and not (self.factor > 0 and self.yarn_fast > 0 and self.yarn_slow > 0 and self.theta > 1):
+            raise ValueError("yarn scaling needs a positive factor and turn counts, and a base above 1")
+
+    def magnitude(self) -> float:
+        """The factor on every cosine and sine (1 unless the scaling scheme has one)."""
+        return 0.1 * math.log(self.factor) + 1.0 if self.scaling_type == "yarn" else 1.0
 
     def inv_freq64(self) -> torch.Tensor:
         """float64 [rotary_dim / 2] ``theta^(-2j / rotary_dim)``, on the CPU, for kernels that form their angles in
-        float64 (plain frequencies only)."""
-        if self.scaling_type != "default":
-            raise ValueError("float64 frequencies exist for the plain rotary encoding")
+        float64 (plain frequencies, or yarn's blend of scaled and unscaled ones)."""
+        if self.scaling_type not in ("default", "yarn"):
+            raise ValueError("float64 frequencies exist for the plain and the yarn rotary encoding")
         d = self.rotary_dim
-        return self.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
+        f = self.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / d)
+        if self.scaling_type == "default":
+            return f
+        orig = float(self.original_max_position_embeddings)
+
+        def turns(t: float) -> float:
+            return d * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+
+        lo = max(math.floor(turns(self.yarn_fast)), 0)
+        hi = min(math.ceil(turns(self.yarn_slow)), d - 1)
+        ramp = ((torch.arange(d // 2, dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        return f / self.factor * ramp + f * (1.0 - ramp)
 
     def inv_freq(self) -> torch.Tensor:
         """float32 [rotary_dim / 2], on the CPU."""
         d = self.rotary_dim
+        if self.scaling_type == "yarn":
+            return self.inv_freq64().to(torch.float32)
         inv = 1.0 / (self.theta ** (torch.arange(0, d, 2, dtype=torch.int64).to(torch.float32) / d))
         if self.scaling_type == "default":
             return inv
