@@ -163,8 +163,8 @@ def test_clamped_experts_weighed_by_the_softmax_over_all(ops, dtype, T, E, top, 
     got = part.forward(None, h.to(DEV)).float().cpu()
     w64 = {k: v.double() for k, v in w.items()}
     idx, wt, s = plain.route(h.double(), w64["router"], top, scale)
-    srt = torch.sort(s, dim=-1, descending=True).values
-    assert top == E or float((srt[:, top - 1] - srt[:, top]).min()) > 1e-6  # no choice rests on a tie
+    srt = torch.sort(h.double() @ w64["router"].T, dim=-1, descending=True).values
+    assert top == E or float((srt[:, top - 1] - srt[:, top]).min()) > 2e-5  # no choice rests on a close call
     assert float(wt.sum(-1).max()) <= scale + 1e-9 and (top == E or float(wt.sum(-1).min()) < 0.99 * scale)  # not renormalised
     want = plain.moe_ff(h.double(), w64, "", mlp)
     assert rel_err(got, want) < (3e-5 if dtype == "float32" else 3e-2)
@@ -231,11 +231,9 @@ def test_differential_attention_at_the_window_and_at_the_kept_positions(ops, dty
             put([n - 1, n - 2], far_at, 0)
         args = (bias, nw, heads, kv, dim, vdim, scale, window, keep, rot, base, lam, eps, mult, raw[:, C:])
         want = two_map_attention(raw[:, :C], *args)
-        if window is not None and rot < dim:
+        if window is not None and rot < dim and far_at >= keep:
             # what the comparison below would miss if the kernels were off by one: the plain result moves a lot
-            for w2, k2, rows in ((window + 1, keep, [far_at + window]), (window, keep - 1, [n - 1]) if keep and keep < far_at else (None, 0, [])):
-                if w2 is None:
-                    continue
+            for w2, k2, rows in [(window + 1, keep, [far_at + window])] + ([(window, keep - 1, [n - 1])] if keep else []):
                 other = two_map_attention(raw[:, :C], bias, nw, heads, kv, dim, vdim, scale, w2, k2, rot, base, lam, eps, mult, raw[:, C:])
                 assert float((other[rows] - want[rows]).abs().max()) > 0.2 * float(want[rows].abs().max()), (w2, k2)
         table, n_pages = paged(n, page, far_at + 1)
@@ -380,7 +378,7 @@ def test_every_constant_shows_in_the_logits(models):
     changing each moves the logits by many times the tolerance of the float32 comparisons."""
     for which, paths in (("a", ["scale", "diff", "mask.size", "mask.keep_first", "rot.dims", "rot.base", "rot.scaling.factor",
                                 "rot.scaling.original", "router.scale", "router.top", "expert.limit", "shared.limit"]),
-                         ("b", ["mask.size", "mask.keep_first", "rot.scaling.fast", "rot.scaling.slow"])):
+                         ("b", ["mask.size", "mask.keep_first"]), ("d", ["mask.size", "rot.scaling.fast", "rot.scaling.slow"])):
         m = models[(which, "dyn")]
         rid, toks = max(m["reqs"].items(), key=lambda kv: len(kv[1]))
         ref = m["want"][rid]
