@@ -2,7 +2,7 @@
 random weights (the metric and configuration of BASELINE.json's configs[2]).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|3|4]
-    python bench.py --design sozurax|daborax|verozen   (another workload, see run_design; the default workload and its output line are unchanged)
+    python bench.py --design sozurax|daborax|verozen|bibalix   (another workload, see run_design; the default workload and its output line are unchanged)
 
 Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8, each request holding a
 2,048-token prompt in the cache, timed on the device with CUDA events around K decode steps
@@ -160,7 +160,7 @@ def prefill_flops(m: dict, T: int, rows: int = 1) -> float:
     return linear + attention
 
 
-TIMED_OPS = ("sum_group_norm", "gelu_gate_rows", "gla_gates", "rotate_scale", "linear_out_f32", "scaled_norm_add", "cast_rows", "add_sinusoid", "clamped_glu", "gated_group_norm", "ssm_prep", "decay_walk",
+TIMED_OPS = ("diff_combine", "head_sigmoid_gate", "moe_logits", "sum_group_norm", "gelu_gate_rows", "gla_gates", "rotate_scale", "linear_out_f32", "scaled_norm_add", "cast_rows", "add_sinusoid", "clamped_glu", "gated_group_norm", "ssm_prep", "decay_walk",
              "sink_attn_prep", "attn_sink", "attn_sink_tc", "silu_cols", "gemm_tcgen05_clamped", "add_layernorm", "add_layernorm_conv1", "short_conv", "polynorm", "gated_recurrence", "latent_prep",
              "rotate_pairs", "latent_attn", "moe_route", "moe_order", "moe_gather", "moe_gemm", "moe_combine",
              "gemm_tcgen05_grouped", "embed_gather", "add_rmsnorm", "rope_kv_write", "rope_kv_write_partials", "linear_decode", "linear_smallm",
@@ -702,6 +702,38 @@ def verozen_configs(name: str) -> dict:
     return dict(verozen=ver, daborax=daborax_configs(name)["daborax"])
 
 
+def bibalix_configs(name: str) -> dict:
+    """Layer sizes for ``--design bibalix``: two sizes that resemble a real model's layers, each as a Bibalix decoder
+    (latent attention with a dense tanh-GELU feed-forward, latent attention with routed clamped experts, differential
+    attention over a window that keeps the first positions, latent attention again; pre-norm under layer norms, the head
+    the embedding table) and as the closest existing model, a Sozurax decoder of latent-attention layers only (the
+    same cached rows, window, attention kernels, layer norms, routed experts with a shared expert) at the same width,
+    depth, vocabulary, head, expert and feed-forward sizes."""
+    sizes = dict(
+        w2048=dict(width=2048, heads=16, kv=4, ff=8192, q_rank=768, experts=16, top=2, expert_ff=1024, shared_ff=2048),
+        w4096=dict(width=4096, heads=32, kv=8, ff=14336, q_rank=1536, experts=32, top=4, expert_ff=1024, shared_ff=2048))
+    z = sizes[name]
+    W, H = z["width"], z["heads"]
+    lat = dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=192, mask=dict(size=1024), scale=192 ** -0.5,
+               rot=dict(base=10000.0, dims=64, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0)))
+    att = dict(heads=H, kv_heads=z["kv"], dim=64, vdim=128, scale=64 ** -0.5, diff=0.3, mask=dict(size=1024, keep_first=4),
+               rot=dict(base=10000.0, dims=64))
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), router=dict(experts=z["experts"], top=z["top"], scale=2.0),
+               shared=dict(ff=z["shared_ff"], limit=7.0))
+    bib = dict(architecture="Bibalix", vocab=32000, width=W, norm=dict(eps=1e-6),
+               layers=[dict(type="latent_attention", mixer=dict(lat), mlp=dict(kind="dense", ff=z["ff"])),
+                       dict(type="latent_attention", mixer=dict(lat), mlp=moe), dict(type="attention", mixer=att, mlp=moe),
+                       dict(type="latent_attention", mixer=dict(lat), mlp=moe)])
+    slat = dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=192, q_rank=z["q_rank"], mask=dict(size=1024),
+                rot=dict(base=10000.0, dims=64), scale=192 ** -0.5)
+    smoe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]),
+                shared=dict(ff=z["shared_ff"]))
+    soz = dict(architecture="Sozurax", vocab=32000, width=W, norm=dict(eps=1e-6), embedding=dict(scale=1.0), canon=dict(taps=4),
+               layers=[dict(type="latent_attention", mixer=dict(slat), mlp=dict(kind="dense", ff=z["ff"]))]
+               + [dict(type="latent_attention", mixer=dict(slat), mlp=smoe) for _ in range(3)])
+    return dict(bibalix=bib, sozurax=soz)
+
+
 def design_configs(name: str) -> dict:
     """Layer sizes for ``--design sozurax``: two sizes that resemble a real model's layers, each as a Sozurax decoder
     (a recurrent layer with a dense feed-forward, a latent-attention layer with routed experts, a second recurrent
@@ -731,7 +763,7 @@ def design_configs(name: str) -> dict:
 
 
 def run_design(args) -> dict:
-    """``--design sozurax|daborax|verozen``: prefill (one 2,048-token prompt in one step) and decode (batch 8 and 64, prompts of
+    """``--design sozurax|daborax|verozen|bibalix``: prefill (one 2,048-token prompt in one step) and decode (batch 8 and 64, prompts of
     2,048 tokens in the cache) of that decoder at two layer sizes beside the closest existing decoder of equal size, random weights,
     bfloat16, with the CUDA-event time of each kind of kernel in one prefill step and one decode step of both."""
     import numpy as np
@@ -745,7 +777,8 @@ def run_design(args) -> dict:
     peaks, peak_src = load_peaks()
     prompt_len, page_size = 2048, 16
     out = dict(design=args.design, dtype="bf16", data="synthetic", peaks=dict(peaks, source=peak_src), sizes={})
-    configs_of = dict(daborax=daborax_configs, sozurax=design_configs, verozen=verozen_configs)[args.design]
+    configs_of = dict(daborax=daborax_configs, sozurax=design_configs, verozen=verozen_configs,
+                      bibalix=bibalix_configs)[args.design]
     for size in ("w2048", "w4096"):
         res = {}
         for arch, cfg in configs_of(size).items():
@@ -762,6 +795,8 @@ def run_design(args) -> dict:
                     b.mixer.lower.uniform_(0.0, 0.9, generator=g)
                 if isinstance(getattr(b, "ffn", None), RoutedExperts):
                     b.ffn.router_w.normal_(0.0, 1.0, generator=g)
+                if getattr(b.mixer, "lam", None) is not None:
+                    b.mixer.lam.fill_(0.5)  # (vectors of ones would make the two maps' factor a difference of overflows)
             vocab = cfg.get("vocab", cfg.get("vocab_size"))
             tg = torch.Generator().manual_seed(0)
 
@@ -856,7 +891,7 @@ def main() -> int:
     ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
                     help="2: the headline metric (default); 3 and 4: the further workloads, see run_further")
     ap.add_argument("--design-arch", default=None, help="with --design: only this arm (the design's name or 'llama')")
-    ap.add_argument("--design", default=None, choices=["sozurax", "daborax", "verozen"],
+    ap.add_argument("--design", default=None, choices=["sozurax", "daborax", "verozen", "bibalix"],
                     help="instead of the headline workload: this design's prefill and decode at two layer sizes beside "
                          "the closest existing decoder of equal size (see run_design)")
     args = ap.parse_args()

@@ -27,14 +27,15 @@ def head_dim_modules(head_dim: int, dtype: str | None = None) -> list[tuple[str,
 def family_modules() -> list[tuple[str, dict | None]]:
     """Kernel modules of parts that only some model families use (layer norm and short convolution, the gated linear
     recurrence, attention over cached latents, routed experts; norms on sublayer outputs, the recurrence with one decay a
-    head and token, attention with capped scores and a sink or with sigmoid weights), at one or two sets of compile-time sizes each: the build
+    head and token, attention with capped scores and a sink or with sigmoid weights, with two maps a head), at one or two sets of compile-time sizes each: the build
     check compiles these; a model compiles the sizes it needs (``Part.kernel_modules``)."""
     return [("post_norm.cu", None), ("decay_recurrence.cu", {"TKB_DR_LANES": 32, "TKB_DR_DPT": 4}),
             ("decay_recurrence.cu", {"TKB_DR_LANES": 16, "TKB_DR_DPT": 8}), ("decay_recurrence.cu", {"TKB_DR_LANES": 8, "TKB_DR_DPT": 16}), ("attention_sink.cu", {"TKB_QK": 128, "TKB_VD": 64}),
             ("attention_sink.cu", {"TKB_QK": 24, "TKB_VD": 40}), ("attention_sink.cu", {"TKB_QK": 64, "TKB_VD": 64, "TKB_SIGMOID": 1}),
             ("norm_conv.cu", None), ("moe.cu", None), ("recurrence.cu", {"TKB_REC_DPT": 16, "TKB_REC_CPT": 1}),
             ("recurrence.cu", {"TKB_REC_DPT": 3, "TKB_REC_CPT": 2}), ("latent_attention.cu", {"TKB_LAT_RANK": 192}),
-            ("attention_mma.cu", {"TKB_HD": 256})]
+            ("attention_mma.cu", {"TKB_HD": 256}), ("attention_sink.cu", {"TKB_QK": 64, "TKB_VD": 128, "TKB_MAPS": 2}),
+            ("attention_sink.cu", {"TKB_QK": 24, "TKB_VD": 40, "TKB_MAPS": 2})]
 
 
 def optional_modules(head_dim: int) -> list[tuple[str, dict | None]]:
