@@ -87,6 +87,12 @@ MODELS = {
                           layers=[dict(lat(5, 8, 24, 16, 40, 0.2, 16, yarn(24, 1000.0, 8.0, 32, 8.0, 2.0)), mlp=moe(32, 2.0, 5, 2, 1.0)),
                                   dict(lat(5, 8, 24, 16, 40, 0.2, 16, yarn(24, 1000.0, 8.0, 32, 8.0, 2.0)), mlp=dense(48)),
                                   dict(lat(2, 20, 10, 28, 21, 0.25, 32, dict(dims=10, base=10000.0)), mlp=moe(24, 1.0, 6, 3, 2.5, (16, 0.5)))])),
+    # sizes that fit no vector load: a width that is no multiple of four, an odd vocabulary, heads of 10 and 6 channels,
+    # a rank of 18, inner sizes of 26 and 22; two experts of which one is chosen
+    "e": dict(page=8, lengths=[70, 21, 44, 2, 33], seed=15,
+              config=dict(architecture="Bibalix", vocab=77, width=70, norm=dict(eps=1e-5),
+                          layers=[dict(att(3, 1, 10, 14, 0.3, 0.35, 19, 2, dict(dims=6, base=200.0)), mlp=moe(22, 1.5, 2, 1, 1.3, (26, 1.0))),
+                                  dict(lat(3, 6, 10, 14, 18, 0.3, 13, yarn(10, 300.0, 2.0, 8, 4.0, 0.5)), mlp=dense(26))])),
 }
 
 MIN_MARGIN = 5e-5  # of a router's logit: far more than float32 sums of a router's width can move one
