@@ -373,7 +373,7 @@ TKB_SINK_EXPORTS(f32, float)
 TKB_SINK_EXPORTS(bf16, __nv_bfloat16)
 
 // ------------------------------------------------------------------------------------------------ tensor cores
-#if (TKB_QK % 16 == 0) && (TKB_VD % 16 == 0) && (TKB_QK <= 256) && (TKB_VD <= 256)
+#if (TKB_QK % 16 == 0) && (TKB_VD % 16 == 0) && (TKB_QK <= 256) && (TKB_VD <= 256) && (TKB_MAPS != 3)
 #define TKB_SINK_TC 1
 namespace {
 
@@ -694,8 +694,11 @@ attn_sink_tiles_kernel(const bf16* __restrict__ q, OutOf<bf16>::type* __restrict
   }
 }
 
-// Single tokens: blockIdx.x = request row (it leaves unless the request brings one token), blockIdx.y = ((key/value
-// head * MAPS) + map) * head tiles + head tile (16 query heads a tile).
+// Single tokens: blockIdx.x = request row (it leaves unless the request brings one token), blockIdx.y = key/value
+// head * head tiles + head tile (16 query heads a tile).  With several maps a head the block's four warps are shared
+// out among the maps (all maps read the tile that the block stages once), and a map's warps share out a tile's keys.
+constexpr int WPM = 4 / MAPS;   // warps a map
+constexpr int KPW = KT / WPM;   // keys of a tile a warp takes
 __global__ void __launch_bounds__(128)
 attn_sink_single_kernel(const bf16* __restrict__ q, OutOf<bf16>::type* __restrict__ out, const bf16* __restrict__ cache,
                         const int* __restrict__ seq_q_start, const int* __restrict__ seq_q_len,
@@ -713,8 +716,8 @@ attn_sink_single_kernel(const bf16* __restrict__ q, OutOf<bf16>::type* __restric
   grid_dependency_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int group = nh / nkv;
-  const int km = blockIdx.y / head_tiles, g0 = (blockIdx.y - km * head_tiles) * 16;
-  const int kvh = km / MAPS, map = km % MAPS, koff = map * QK, nhm = nh * MAPS;
+  const int kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y - kvh * head_tiles) * 16;
+  const int map = warp / WPM, wsub = warp % WPM, koff = map * QK, nhm = nh * MAPS;
   const int gn = min(16, group - g0);
   const int tok = seq_q_start[s];
   const int p = seq_kv_len[s] - 1;
@@ -738,7 +741,7 @@ attn_sink_single_kernel(const bf16* __restrict__ q, OutOf<bf16>::type* __restric
     sm[hh] = score_map(scale * (head_scale ? head_scale[head] : 1.f), softcap, head_bias ? head_bias[head] : 0.f);
     // (the sigmoid form: every share has maximum 0, and ONE share carries the sum 1, so the merges below only add)
     m[hh] = SIGMOID ? 0.f : (sinks ? sinks[head] * LOG2E : NEG_BIG);
-    l[hh] = ((SIGMOID || sinks) && split == 0 && warp == 0 && t == 0) ? 1.f : 0.f;  // the sink counts once: in one warp's sums
+    l[hh] = ((SIGMOID || sinks) && split == 0 && wsub == 0 && t == 0) ? 1.f : 0.f;  // the sink counts once: in one warp's sums
   }
   float o[VT][4];
 #pragma unroll
@@ -770,11 +773,11 @@ attn_sink_single_kernel(const bf16* __restrict__ q, OutOf<bf16>::type* __restric
       cp_async_wait<0>();
     }
     __syncthreads();
-    const int key0 = tile_key0(it0 + it) + warp * 16;
+    const int key0 = tile_key0(it0 + it) + wsub * KPW;
     const int last = tile_last(it0 + it);
     if (key0 <= last) {
       const int tl[2] = {tile_first(it0 + it), tile_first(it0 + it)}, th[2] = {last, last};
-      attend<2, true>(cur, warp * 16, key0, qf, o, m, l, tl, th, sm, lane, koff, 0);
+      attend<KPW / 8, true>(cur, wsub * KPW, key0, qf, o, m, l, tl, th, sm, lane, koff, 0);
     }
     __syncthreads();
   }
@@ -803,19 +806,19 @@ attn_sink_single_kernel(const bf16* __restrict__ q, OutOf<bf16>::type* __restric
     sml[(warp * 16 + g + 8) * 2 + 1] = l[1];
   }
   __syncthreads();
-  for (int idx = tid; idx < gn * VD; idx += 128) {
-    const int r = idx / VD, d = idx - r * VD;
+  for (int idx = tid; idx < MAPS * gn * VD; idx += 128) {
+    const int mp = idx / (gn * VD), r = (idx - mp * gn * VD) / VD, d = idx - (mp * gn + r) * VD;
     float mm = NEG_BIG;
 #pragma unroll
-    for (int w = 0; w < 4; w++) mm = fmaxf(mm, sml[(w * 16 + r) * 2]);
+    for (int w = mp * WPM; w < (mp + 1) * WPM; w++) mm = fmaxf(mm, sml[(w * 16 + r) * 2]);
     float acc = 0.f, ll = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; w++) {
+    for (int w = mp * WPM; w < (mp + 1) * WPM; w++) {
       const float f = exp2f(sml[(w * 16 + r) * 2] - mm);
       acc += f * so[(w * 16 + r) * SO + d];
       ll += f * sml[(w * 16 + r) * 2 + 1];
     }
-    const int head = (kvh * group + g0 + r) * MAPS + map;
+    const int head = (kvh * group + g0 + r) * MAPS + mp;
     if (splits == 1) {
       out[((size_t)tok * nhm + head) * VD + d] = from_float<OutOf<bf16>::type>(ll > 0.f ? acc / ll : 0.f);
     } else {  // this split's share: sums relative to its own maximum, for attn_sink_merge
@@ -866,7 +869,7 @@ TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache
   if (n_tokens <= 0 || n_seqs <= 0) return 0;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || keep_first < 0) return -2;
   const int head_tiles = (nh / nkv + 15) / 16;
-  if (nh * MAPS > 65535 || nkv * MAPS * head_tiles > 65535) return -3;
+  if (nh * MAPS > 65535 || nkv * head_tiles > 65535) return -3;
   if (TC_SMEM > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attn_sink_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
     if (e == cudaSuccess)
@@ -877,7 +880,7 @@ TKB_EXPORT int tkb_attn_sink_tc_bf16(const void* q, void* out, const void* cache
   if (splits < 1 || part == nullptr) splits = 1;
   if (splits > 64) return -2;
   if (singles) {
-    rc = launch_pdl(attn_sink_single_kernel, dim3(n_seqs, nkv * MAPS * head_tiles, splits), dim3(128), TC_SMEM,
+    rc = launch_pdl(attn_sink_single_kernel, dim3(n_seqs, nkv * head_tiles, splits), dim3(128), TC_SMEM,
                     (cudaStream_t)st, (const bf16*)q, (TO*)out, (const bf16*)cache, seq_q_start, seq_q_len, seq_kv_len,
                     page_indptr, page_ids, sinks, nh, nkv, head_tiles, page_size, scale, softcap, window, keep_first,
                     num_pages, status, part, head_scale, head_bias);

@@ -1456,10 +1456,10 @@ def attn_sink(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, token_seq
         _ptr(status), _ptr(head_scale), _ptr(head_bias), _stream()), "attn_sink")
 
 
-def can_use_attn_sink_tc(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+def can_use_attn_sink_tc(dtype: torch.dtype, dim: int, vdim: int, maps: int = 1) -> bool:
     """The tensor-core kernels of csrc/attention_sink.cu take bfloat16 rows whose key and value sizes are multiples of 16
-    up to 256."""
-    return dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and dim <= 256 and vdim <= 256
+    up to 256, with one, two or four maps a head (a block's four warps are shared out among the maps)."""
+    return dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and dim <= 256 and vdim <= 256 and maps in (1, 2, 4)
 
 
 def attn_sink_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor,
@@ -1475,7 +1475,7 @@ def attn_sink_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, seq_q_
     _head_vectors(n_heads * maps, "attn_sink_tc", head_scale, head_bias)
     _need(not (sigmoid and sinks is not None), "attn_sink_tc: the sigmoid form has no sink")
     T = q.shape[0]
-    _need(can_use_attn_sink_tc(cache.dtype, dim, vdim), "attn_sink_tc: bfloat16 rows, key and value sizes multiples of 16")
+    _need(can_use_attn_sink_tc(cache.dtype, dim, vdim, maps), "attn_sink_tc: bfloat16 rows, key and value sizes multiples of 16")
     _need(q.is_contiguous() and q.shape[1] == n_heads * maps * dim and q.dtype == cache.dtype
           and _sink_out_ok(out, T, n_heads, vdim, maps, cache.dtype), "attn_sink_tc: q and out")
     _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (n_kv_heads, page_size, maps * dim + vdim), "attn_sink_tc: cache rows")
@@ -1486,7 +1486,7 @@ def attn_sink_tc(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, seq_q_
     if singles:
         from tokasaurus_b200.kernels.device import device_limits
 
-        blocks = n_seqs * n_kv_heads * maps * ((n_heads // n_kv_heads + 15) // 16)
+        blocks = n_seqs * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)  # (a block serves every map of its heads)
         splits = max(1, min(8, (2 * device_limits(q.device).sm_count) // max(1, blocks)))
         if window:
             splits = min(splits, max(1, (window + 63) // 64))

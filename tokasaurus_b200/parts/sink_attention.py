@@ -150,7 +150,7 @@ class SinkAttention(Mixer):
                            rot_dims=self.rotary.rotary_dim if self.rot_freq is not None else 0,
                            rot_pairs=self.rotary_pairs, values_are_keys=self.values_are_keys, sigmoid=self.sigmoid, maps=M)
         out_dtype = h.dtype if M == 1 else torch.float32  # several maps' outputs stay unrounded for what combines them
-        if ops.can_use_attn_sink_tc(h.dtype, d, e):
+        if ops.can_use_attn_sink_tc(h.dtype, d, e, M):
             # bfloat16: every token on the tensor cores (single tokens and portions by a kernel each); wanted rows are
             # cut out afterwards
             attn = torch.empty((T, H * M * e), dtype=out_dtype, device=h.device)
