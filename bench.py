@@ -716,7 +716,7 @@ def bibalix_configs(name: str) -> dict:
     W, H = z["width"], z["heads"]
     lat = dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=192, mask=dict(size=1024), scale=192 ** -0.5,
                rot=dict(base=10000.0, dims=64, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0)))
-    att = dict(heads=H, kv_heads=z["kv"], dim=64, vdim=128, scale=64 ** -0.5, diff=0.3, mask=dict(size=1024, keep_first=4),
+    att = dict(heads=H, kv_heads=z["kv"], dim=64, vdim=128, scale=64 ** -0.5, diff=0.2, mask=dict(size=1024, keep_first=8),
                rot=dict(base=10000.0, dims=64))
     moe = dict(kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), router=dict(experts=z["experts"], top=z["top"], scale=2.0),
                shared=dict(ff=z["shared_ff"], limit=7.0))

@@ -71,7 +71,7 @@ MODELS = {
     "b": dict(page=16, lengths=[300, 150, 40, 210, 33, 64], seed=12,
               config=dict(architecture="Bibalix", vocab=113, width=128, norm=dict(eps=1e-6),
                           layers=[dict(att(8, 1, 32, 64, 0.18, 0.3, 45, 70, dict(dims=32, base=10000.0)), mlp=moe(64, 2.0, 8, 4, 2.0, (64, 1.0))),
-                                  dict(lat(4, 32, 16, 32, 48, 0.15, 33, yarn(16, 20000.0, 4.0, 64)), mlp=dense(96)),
+                                  dict(lat(4, 32, 16, 32, 48, 0.15, 33, yarn(16, 30000.0, 3.0, 64)), mlp=dense(96)),
                                   dict(att(2, 2, 64, 16, 0.125, 0.6, 16, 1, dict(dims=32, base=1e6)), mlp=moe(72, 1.2, 3, 3, 0.7, (40, 2.5)))])),
     # attention only: no window at all, a window that keeps nothing, no rotation, one head, three key/value heads of
     # six; dense feed-forwards and none

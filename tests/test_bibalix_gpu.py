@@ -50,7 +50,7 @@ def paged(n_tokens, page, seed):
 # ------------------------------------------------------------------------------------------------ mechanisms alone
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,dim,rot,dims,scaling", [(3, 16, 8, 8, (2.0, 16, 4.0, 1.0)), (2, 12, 6, 4, None),
-                                                        (5, 8, 24, 24, (8.0, 32, 8.0, 2.0)), (1, 32, 64, 32, (4.0, 512, 32.0, 1.0))])
+                                                        (5, 8, 24, 24, (8.0, 32, 8.0, 2.0)), (1, 32, 64, 32, (3.0, 256, 16.0, 1.0))])
 def test_rotation_in_halves_with_blended_frequencies(ops, dtype, heads, dim, rot, dims, scaling):
     """The rotated share of every query head, at positions into the thousands: channel i with channel i + dims / 2,
     frequencies blended between scaled and unscaled, sine and cosine times the scheme's factor."""
@@ -192,7 +192,7 @@ def two_map_attention(raw, bias, nw, heads, kv, dim, vdim, scale, window, keep, 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("dim,vdim,rot,page,heads,kv,window,keep", [
     (16, 32, 8, 16, 4, 2, 37, 3), (32, 64, 32, 16, 8, 1, 45, 70), (24, 40, 24, 8, 2, 2, 50, 9), (64, 16, 32, 16, 2, 2, 16, 1),
-    (48, 96, 48, 16, 20, 1, 136, 4), (16, 16, 0, 8, 3, 3, 64, 64), (32, 32, 16, 16, 2, 1, None, 0)])
+    (48, 80, 48, 16, 20, 1, 130, 5), (16, 16, 0, 8, 3, 3, 64, 64), (32, 32, 16, 16, 2, 1, None, 0)])
 def test_differential_attention_at_the_window_and_at_the_kept_positions(ops, dtype, dim, vdim, rot, page, heads, kv, window, keep):
     """Two maps a head over the same values, a window that keeps the first positions in sight.  Made-up keys that
     made-up queries score far above all others stand (a) a window back from two neighbouring queries, of which one

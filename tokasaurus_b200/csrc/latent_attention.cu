@@ -197,6 +197,9 @@ __device__ __forceinline__ float dot_span<__nv_bfloat16>(const __nv_bfloat16* __
 // One warp owns one (token, head).  A token at position p sees the rows of positions max(0, p - window + 1) .. p of
 // its own request (window <= 0: all); the step's own rows are in the cache already.  Lane j scores row base + j;
 // after the warp-wide running maximum and sum are brought up to date, lane d accumulates latent elements d, d + 32, ...
+// splits > 1 (steps of few rows, which would leave most SMs idle): the visible rows of a (token, head) are shared out
+// among blockIdx.z warps in runs of a multiple of 32 rows; each leaves its sums, maximum (log2 units) and weight sum in
+// part[((row * heads + head) * splits + split) * (RANK + 2)], and latent_attn_merge puts them together.
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 latent_attn_simt_kernel(const T* __restrict__ q_abs, long long qa_token_stride, long long qa_head_stride,
@@ -204,7 +207,8 @@ latent_attn_simt_kernel(const T* __restrict__ q_abs, long long qa_token_stride, 
                         T* __restrict__ out, const T* __restrict__ cache, const int* __restrict__ token_seq,
                         const int* __restrict__ positions, const int* __restrict__ page_indptr,
                         const int* __restrict__ page_ids, const int* __restrict__ rows, int n_heads, int page_size,
-                        float scale_log2, int window, int num_pages, int* __restrict__ status) {
+                        float scale_log2, int window, int num_pages, int* __restrict__ status, int splits,
+                        float* __restrict__ part) {
   extern __shared__ float qs_all[];  // [WARPS][RANK + rot]
   trigger_dependents();
   grid_dependency_wait();
@@ -231,9 +235,15 @@ latent_attn_simt_kernel(const T* __restrict__ q_abs, long long qa_token_stride, 
   float acc[DPL];
 #pragma unroll
   for (int i = 0; i < DPL; i++) acc[i] = 0.f;
-  for (int base = lo; base <= p; base += 32) {
+  int first = lo, last = p;
+  if (splits > 1) {
+    const int per = (((p - lo + 1) + splits - 1) / splits + 31) & ~31;
+    first = lo + (int)blockIdx.z * per;
+    last = min(p, first + per - 1);
+  }
+  for (int base = first; base <= last; base += 32) {
     const int j = base + lane;
-    const bool live = j <= p;
+    const bool live = j <= last;
     long long rowoff = 0;
     float sc = -FLT_MAX;
     if (live) {
@@ -250,7 +260,7 @@ latent_attn_simt_kernel(const T* __restrict__ q_abs, long long qa_token_stride, 
     m = m_new;
 #pragma unroll
     for (int i = 0; i < DPL; i++) acc[i] *= alpha;
-    const int nlive = (p - base + 1) < 32 ? (p - base + 1) : 32;
+    const int nlive = (last - base + 1) < 32 ? (last - base + 1) : 32;
     for (int jj = 0; jj < nlive; jj++) {
       const float pv = __shfl_sync(0xffffffffu, pj, jj);
       const long long ro = __shfl_sync(0xffffffffu, rowoff, jj);
@@ -262,12 +272,43 @@ latent_attn_simt_kernel(const T* __restrict__ q_abs, long long qa_token_stride, 
       }
     }
   }
+  if (splits > 1) {
+    float* pr = part + (((size_t)blockIdx.x * n_heads + h) * splits + blockIdx.z) * (RANK + 2);
+#pragma unroll
+    for (int i = 0; i < DPL; i++) {
+      const int d = lane + 32 * i;
+      if (d < RANK) pr[d] = acc[i];
+    }
+    if (lane == 0) {
+      pr[RANK] = m;
+      pr[RANK + 1] = l;
+    }
+    return;
+  }
   const float inv_l = l > 0.f ? 1.f / l : 0.f;
   T* orow = out + ((size_t)blockIdx.x * n_heads + h) * RANK;
 #pragma unroll
   for (int i = 0; i < DPL; i++) {
     const int d = lane + 32 * i;
     if (d < RANK) orow[d] = from_float<T>(acc[i] * inv_l);
+  }
+}
+
+// The shares of a (row, head) put together: grid (rows, heads).
+template <typename T>
+__global__ void latent_attn_merge_kernel(const float* __restrict__ part, T* __restrict__ out, int n_heads, int splits) {
+  trigger_dependents();
+  grid_dependency_wait();
+  const float* pr = part + ((size_t)blockIdx.x * n_heads + blockIdx.y) * splits * (RANK + 2);
+  float mm = -FLT_MAX;
+  for (int z = 0; z < splits; z++) mm = fmaxf(mm, pr[z * (RANK + 2) + RANK]);
+  float ll = 0.f;
+  for (int z = 0; z < splits; z++) ll += exp2f(pr[z * (RANK + 2) + RANK] - mm) * pr[z * (RANK + 2) + RANK + 1];
+  const float inv = ll > 0.f ? 1.f / ll : 0.f;
+  for (int d = threadIdx.x; d < RANK; d += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < splits; z++) acc += exp2f(pr[z * (RANK + 2) + RANK] - mm) * pr[z * (RANK + 2) + d];
+    out[((size_t)blockIdx.x * n_heads + blockIdx.y) * RANK + d] = from_float<T>(acc * inv);
   }
 }
 
@@ -298,19 +339,24 @@ template <typename T>
 int attn_launch(const void* q_abs, long long qa_ts, long long qa_hs, const void* q_rot, long long qr_ts, long long qr_hs,
                 int rot, void* out, const void* cache, const int* token_seq, const int* positions,
                 const int* page_indptr, const int* page_ids, const int* rows, int n_rows, int n_heads, int page_size,
-                float scale, int window, int num_pages, int* status, cudaStream_t st) {
+                float scale, int window, int num_pages, int* status, int splits, float* part, cudaStream_t st) {
   if (n_rows <= 0) return 0;
   if (n_heads <= 0 || page_size <= 0 || rot < 0) return -2;
+  if (splits < 1 || part == nullptr) splits = 1;
+  if (splits > 64 || n_heads > 65535) return -2;
   const int hb = (n_heads + WARPS - 1) / WARPS;
   if (hb > 65535) return -3;
   const size_t smem = (size_t)WARPS * (RANK + rot) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(latent_attn_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return launch_pdl(latent_attn_simt_kernel<T>, dim3(n_rows, hb), dim3(WARPS * 32), smem, st, (const T*)q_abs, qa_ts,
-                    qa_hs, (const T*)q_rot, qr_ts, qr_hs, rot, (T*)out, (const T*)cache, token_seq, positions,
-                    page_indptr, page_ids, rows, n_heads, page_size, scale * 1.4426950408889634f, window, num_pages,
-                    status);
+  int rc = launch_pdl(latent_attn_simt_kernel<T>, dim3(n_rows, hb, splits), dim3(WARPS * 32), smem, st, (const T*)q_abs,
+                      qa_ts, qa_hs, (const T*)q_rot, qr_ts, qr_hs, rot, (T*)out, (const T*)cache, token_seq, positions,
+                      page_indptr, page_ids, rows, n_heads, page_size, scale * 1.4426950408889634f, window, num_pages,
+                      status, splits, part);
+  if (rc != 0 || splits == 1) return rc;
+  return launch_pdl(latent_attn_merge_kernel<T>, dim3(n_rows, n_heads), dim3(RANK >= 128 ? 128 : 64), 0, st,
+                    (const float*)part, (T*)out, n_heads, splits);
 }
 
 }  // namespace
@@ -345,10 +391,10 @@ int attn_launch(const void* q_abs, long long qa_ts, long long qa_hs, const void*
                                             const int* token_seq, const int* positions, const int* page_indptr,        \
                                             const int* page_ids, const int* rows, int n_rows, int n_heads,             \
                                             int page_size, float scale, int window, int num_pages, int* status,        \
-                                            void* st) {                                                                \
+                                            int splits, float* part, void* st) {                                       \
     return attn_launch<T>(q_abs, qa_ts, qa_hs, q_rot, qr_ts, qr_hs, rot, out, cache, token_seq, positions,             \
                           page_indptr, page_ids, rows, n_rows, n_heads, page_size, scale, window, num_pages, status,   \
-                          (cudaStream_t)st);                                                                           \
+                          splits, part, (cudaStream_t)st);                                                             \
   }
 
 TKB_LATENT_EXPORTS(f32, float)

@@ -923,12 +923,26 @@ def latent_attn(q_abs: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, cac
     _need(q_abs.dtype == cache.dtype and q_rot.dtype == cache.dtype and out.dtype == cache.dtype, "latent_attn: one type")
     _need(cache.is_contiguous() and tuple(cache.shape[1:]) == (1, page_size, rank + rot), "latent_attn: cache layout")
     _need(out.is_contiguous() and tuple(out.shape) == (n_rows, nh, rank), "latent_attn: out [rows, heads, rank]")
+    # few rows (the wanted rows of a prompt's last layer, decode steps of a float32 engine): a (row, head)'s visible
+    # rows are shared out among warps until the SMs hold eight each (a function of the step's shape only, so that the
+    # same step replays from a graph); a small kernel puts the shares together
+    from tokasaurus_b200.kernels.device import device_limits
+
+    splits, part = 1, None
+    warps = n_rows * nh
+    sms = device_limits(q_abs.device).sm_count
+    if 0 < warps < 4 * sms:
+        splits = min(32, (8 * sms) // warps)
+        if window:
+            splits = min(splits, max(1, -(-window // 32)))
+        if splits > 1:
+            part = torch.empty((warps * splits * (rank + 2),), dtype=torch.float32, device=q_abs.device)
     f = _fn(_libs.get("latent_attention.cu", TKB_LAT_RANK=rank), f"tkb_latent_attn_simt_{_suffix(cache.dtype)}")
     _check(f(_ptr(q_abs), ctypes.c_longlong(q_abs.stride(0)), ctypes.c_longlong(q_abs.stride(1)), _ptr(q_rot),
              ctypes.c_longlong(q_rot.stride(0)), ctypes.c_longlong(q_rot.stride(1)), c_int(rot), _ptr(out), _ptr(cache),
              _ptr(token_seq), _ptr(positions), _ptr(page_indptr), _ptr(page_ids), _ptr(rows), c_int(n_rows), c_int(nh),
-             c_int(page_size), c_float(scale), c_int(window or 0), c_int(cache.shape[0]), _ptr(status), _stream()),
-           "latent_attn")
+             c_int(page_size), c_float(scale), c_int(window or 0), c_int(cache.shape[0]), _ptr(status), c_int(splits),
+             _ptr(part), _stream()), "latent_attn")
 
 
 # ---------------------------------------------------------------------------------------------
