@@ -453,6 +453,29 @@ def test_greedy_generation_through_the_entry_point(models, graphs, which):
     assert not cache.requests and cache.num_free_pages() == [g.allocator.num_pages for g in cache.groups]
 
 
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_bfloat16_generation_from_graphs_equals_kernel_by_kernel(models, which):
+    """The serving precision: decode steps replayed from CUDA graphs choose the tokens that the same steps choose kernel by
+    kernel (the same kernels on the same data), and every chosen token is near the plain statement's best at its place."""
+    from tokasaurus_b200.engine.engine import Engine
+
+    m = models[(which, "tier")]
+    V = m["config"]["vocab"]
+    prompts = [cuttings.random_tokens(n, V, 500 + n) for n in (70, 5, 33, 120)]
+    got = []
+    for graphs in (False, True):
+        eng = Engine(model=str(m["folder"]), dtype="bfloat16", page_size=m["page"], kv_cache_num_tokens=1024,
+                     max_tokens_per_forward=64, max_seqs_per_forward=4, allocator_sanity_checks=True, use_cudagraphs=graphs)
+        got.append([o.completion_ids for o in eng.generate(prompts, max_num_tokens=12, ignore_eos=True)])
+        del eng
+    assert got[0] == got[1]
+    for p, ids in zip(prompts, got[0]):
+        logits = plain.forward(m["config"], m["weights"], p + ids[:-1])[len(p) - 1:]
+        top = float(logits.abs().max())
+        for i, t in enumerate(ids):
+            assert float(logits[i, t]) >= float(logits[i].max()) - 0.05 * top, (which, i)
+
+
 def test_command_line_generates(models, tmp_path):
     """``toka model=<folder>`` picks the model class from config.json and generates."""
     import json
