@@ -474,23 +474,24 @@ def test_tc_attention_mixed_batch(ops, hd, nh, nkv, ps, window):
     torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
     got2, _ = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed=nh + ps, tc=True)
     assert torch.equal(got, got2)
-
-
-@pytest.mark.xfail(strict=False, reason="one head a block: the kernel for heads of 128 gives wrong rows for a tile's last 32 "
-                                        "queries in about one run in twenty of the shape (6, 3, 4, 300); the engine's "
-                                        "planner does not ask for this form")
-@pytest.mark.parametrize("hd", [64, 128])
-@pytest.mark.parametrize("nh,nkv,ps,window", [(32, 8, 16, None), (3, 1, 8, None), (5, 5, 5, None), (4, 2, 64, 17),
-                                              (6, 3, 4, 300), (8, 2, 16, 128), (4, 2, 256, None), (2, 1, 128, 200)])
-def test_tc_attention_one_head_a_block(ops, hd, nh, nkv, ps, window):
-    """One head a block instead of two (for steps with few query tiles): the same arithmetic a head."""
-    lens_q = [1, 70, 2, 130, 1, 64, 128, 300, 129]
-    lens_kv = [777, 70, 259, 400, 256, 64, 128, 1000, 129]
-    got, want = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed=nh + ps, tc=True)
+    # one head a block instead of two (what a step with few query tiles asks for): the same arithmetic a head
     got3, _ = run_mma_attention(ops, lens_q, lens_kv, nh, nkv, hd, ps, window, seed=nh + ps, tc=True, single_heads=True)
     assert not torch.isnan(got3).any()
     torch.testing.assert_close(got3, want, rtol=1.6e-2, atol=1.2e-2)
     torch.testing.assert_close(got3.float(), got.float(), rtol=0, atol=2e-2 * want.abs().max().item())
+
+
+def test_tc_attention_a_warp_that_scales_its_rows_is_waited_for(ops):
+    """Head size 128, pages of 4 (every tile gathered, so the tensor pipe is often idle), a window of 300: in a 128-query
+    tile of the 300-token portion the last 32 queries see their first key two tiles after the others, and their warp
+    scales its rows of the output while the other warps are already a tile ahead.  Sixty runs, one head a block: their
+    arrivals must not be counted for the late warp's tile (the product over its unwritten weights gave wrong rows in
+    about one run in twenty)."""
+    lens_q = [1, 70, 2, 130, 1, 64, 128, 300, 129]
+    lens_kv = [777, 70, 259, 400, 256, 64, 128, 1000, 129]
+    for _ in range(60):
+        got, want = run_mma_attention(ops, lens_q, lens_kv, 6, 3, 128, 4, 300, seed=10, tc=True, single_heads=True)
+        torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.2e-2)
 
 
 @pytest.mark.parametrize("hd", [64, 128])

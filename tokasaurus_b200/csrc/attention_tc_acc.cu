@@ -390,6 +390,10 @@ attn_prefill_acc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       l += whole ? row_exp<false>(sj, prow, r, lo, span, scale_log2, -ref) : row_exp<true>(sj, prow, r, lo, span, scale_log2, -ref);
       tcgen05_fence_before();
       fence_proxy_async();
+      // S_{j+1} is in tensor memory before S_j has been read by everyone (two S tiles), so a warp can be a whole tile
+      // ahead of one that is still scaling its rows of O: its arrival for tile j must not count toward tile j - 1's
+      // 128 (the product of tile j - 1 would start without the late warp's P and over its unscaled O)
+      if (j >= 1 && !mbar_wait(&p_full[hh], (j - 1) & 1)) { ok = false; break; }
       mbar_arrive(&p_full[hh]);
     }
     if (ok) ok = mbar_wait(&pv_done[hh][(n_kv_tiles - 1) & 1], ((n_kv_tiles - 1) >> 1) & 1);

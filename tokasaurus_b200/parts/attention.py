@@ -166,12 +166,8 @@ class AttentionPlanning:
         return self.n_kv_heads * ((self.n_heads // self.n_kv_heads + 15) // 16)
 
     def plan(self, host, capacity=None):
-        # (head_blocks=0: the portions' kernel never runs one head a block.  In that form the tcgen05 kernel for heads of
-        # 128 has given wrong rows for the last 32 queries of a tile in about one run in twenty of one test shape
-        # (pages of 4, a window of 300, a 300-token portion at context 1,000); the cause is not found, so steps with few
-        # query tiles keep blocks of two heads, which have not shown it.)
         return plan_attention(host, self.window, capacity, self._blocks_per_item(), self._query_tile(),
-                              self.block_slots, 0)
+                              self.block_slots, self.sm_count // self.n_heads)
 
     def plan_capacity(self, n_requests: int) -> dict:
         """The most work items ``plan`` can make for a step of ``n_requests`` single-token requests, whatever
